@@ -1,0 +1,20 @@
+"""helion_b200: B200-native (sm_100a) FP8 GEMM and FP8 attention behind Helion's example signatures.
+
+Public surface:
+    fp8_gemm, fp8_attention         -- operators on torch CUDA tensors (helion_b200.ops)
+    DropInKernel                    -- object with the protocol of helion.runtime.kernel.Kernel
+                                       that the reference's test and benchmark harness touch
+There is no CPU, Triton or PyTorch fallback: calls fail loudly when the CUDA library is missing.
+"""
+from __future__ import annotations
+
+from ._lib import DeviceWaitTimeout, LibraryNotBuiltError
+from .ops import attention_into, fp8_attention, fp8_gemm
+
+__all__ = [
+    "fp8_gemm",
+    "fp8_attention",
+    "attention_into",
+    "DeviceWaitTimeout",
+    "LibraryNotBuiltError",
+]

@@ -1,0 +1,312 @@
+// C ABI of the library (declared in include/helion_b200.h): argument validation, per-device
+// context, error text.  The kernels and their launchers live in fp8_gemm.cu / fp8_attention.cu.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "host.h"
+
+namespace hb {
+
+namespace {
+constexpr int kMaxDevices = 64;
+DeviceCtx g_ctx[kMaxDevices];
+std::mutex g_ctx_mutex;
+thread_local std::string g_last_error;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+}  // namespace
+
+int set_error(int code, const std::string& text) {
+  g_last_error = text;
+  return code;
+}
+
+const char* last_error_text() { return g_last_error.c_str(); }
+
+DeviceCtx* get_device_ctx(int device) {
+  if (device < 0 || device >= kMaxDevices) {
+    set_error(HB200_ERR_CUDA, "device index out of range");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_ctx_mutex);
+  DeviceCtx& c = g_ctx[device];
+  if (c.initialised) {
+    if (c.init_error != 0) {
+      set_error(c.init_error, "device initialisation failed earlier (not an sm_100 GPU, or a CUDA error)");
+      return nullptr;
+    }
+    return &c;
+  }
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || device >= count) {
+    // Not cached: a later call may find a GPU.
+    set_error(HB200_ERR_CUDA, std::string("no such CUDA device: ") + (e != cudaSuccess ? cudaGetErrorString(e) : "index beyond device count"));
+    return nullptr;
+  }
+  DeviceGuard guard(device);
+  c.initialised = true;
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess) {
+    c.init_error = HB200_ERR_CUDA;
+    set_error(HB200_ERR_CUDA, std::string("cudaGetDeviceProperties: ") + cudaGetErrorString(e));
+    return nullptr;
+  }
+  c.num_sms = prop.multiProcessorCount;
+  c.cc_major = prop.major;
+  c.cc_minor = prop.minor;
+  if (prop.major != 10) {
+    c.init_error = HB200_ERR_UNSUPPORTED_ARCH;
+    set_error(HB200_ERR_UNSUPPORTED_ARCH, "this library holds sm_100a code only; device is sm_" +
+                                              std::to_string(prop.major) + std::to_string(prop.minor));
+    return nullptr;
+  }
+  e = cudaHostAlloc(reinterpret_cast<void**>(&c.status_host), 64, cudaHostAllocMapped);
+  if (e == cudaSuccess) {
+    std::memset(c.status_host, 0, 64);
+    e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&c.status_dev), c.status_host, 0);
+  }
+  if (e != cudaSuccess) {
+    c.init_error = HB200_ERR_CUDA;
+    set_error(HB200_ERR_CUDA, std::string("status word allocation: ") + cudaGetErrorString(e));
+    return nullptr;
+  }
+  if (g_encode_tiled == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || fn == nullptr || qres != cudaDriverEntryPointSuccess) {
+      c.init_error = HB200_ERR_CUDA;
+      set_error(HB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+      return nullptr;
+    }
+    g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  return &c;
+}
+
+int device_init_error(int device) {
+  if (device >= 0 && device < kMaxDevices && g_ctx[device].init_error != 0) return g_ctx[device].init_error;
+  return HB200_ERR_CUDA;
+}
+
+int encode_tmap(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, int rank, const uint64_t* dims,
+                const uint64_t* strides, const uint32_t* box, CUtensorMapSwizzle swizzle) {
+  if (g_encode_tiled == nullptr) return set_error(HB200_ERR_CUDA, "tensor-map encoder not initialised");
+  cuuint64_t gdims[5];
+  cuuint64_t gstrides[5];
+  cuuint32_t gbox[5];
+  cuuint32_t gelem[5];
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    gelem[i] = 1;
+    if (i + 1 < rank) gstrides[i] = strides[i];
+  }
+  CUresult r = g_encode_tiled(map, dtype, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims, gstrides,
+                              gbox, gelem, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[256];
+    std::snprintf(buf, sizeof(buf),
+                  "cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu x %llu, stride0 %llu, box %u x %u)",
+                  static_cast<int>(r), rank, (unsigned long long)dims[0], (unsigned long long)(rank > 1 ? dims[1] : 0),
+                  (unsigned long long)(rank > 1 ? strides[0] : 0), box[0], rank > 1 ? box[1] : 0);
+    return set_error(HB200_ERR_CUDA, buf);
+  }
+  return HB200_OK;
+}
+
+int encode_tmap_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                   const uint32_t* box, CUtensorMapSwizzle swizzle) {
+  return encode_tmap(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, base, rank, dims, strides, box, swizzle);
+}
+
+}  // namespace hb
+
+using namespace hb;
+
+static int ctx_error_code(int device) {
+  return hb::device_init_error(device);
+}
+
+extern "C" {
+
+int hb200_version(void) { return HB200_VERSION; }
+
+const char* hb200_last_error(void) { return last_error_text(); }
+
+int hb200_num_sms(int device) {
+  DeviceCtx* ctx = get_device_ctx(device);
+  return ctx == nullptr ? HB200_ERR_CUDA : ctx->num_sms;
+}
+
+int hb200_read_status(int device, uint32_t* site) {
+  DeviceCtx* ctx = get_device_ctx(device);
+  if (ctx == nullptr) return HB200_ERR_CUDA;
+  uint32_t v = *reinterpret_cast<volatile uint32_t*>(ctx->status_host);
+  if (site != nullptr) *site = v;
+  if (v != 0) {
+    char buf[128];
+    std::snprintf(buf, sizeof(buf), "a device-side wait ran out: site %u, block %u", v >> 16, v & 0xffffu);
+    return set_error(HB200_ERR_TIMEOUT, buf);
+  }
+  return HB200_OK;
+}
+
+int hb200_reset_status(int device) {
+  DeviceCtx* ctx = get_device_ctx(device);
+  if (ctx == nullptr) return HB200_ERR_CUDA;
+  *reinterpret_cast<volatile uint32_t*>(ctx->status_host) = 0;
+  return HB200_OK;
+}
+
+int hb200_num_configs(int op) {
+  if (op == HB200_OP_GEMM) return gemm_num_configs();
+  if (op == HB200_OP_ATTENTION) return attn_num_configs();
+  return set_error(HB200_ERR_BAD_CONFIG, "unknown op");
+}
+
+int hb200_describe_config(int op, int cfg_id, char* buf, int buf_len) {
+  if (buf == nullptr || buf_len <= 0) return set_error(HB200_ERR_BAD_CONFIG, "no buffer");
+  if (op == HB200_OP_GEMM) return gemm_describe_config(cfg_id, buf, buf_len);
+  if (op == HB200_OP_ATTENTION) return attn_describe_config(cfg_id, buf, buf_len);
+  return set_error(HB200_ERR_BAD_CONFIG, "unknown op");
+}
+
+size_t hb200_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int cfg_id) {
+  return gemm_workspace_bytes(M, N, K, out_dtype, cfg_id);
+}
+
+int hb200_fp8_gemm_select_config(int64_t M, int64_t N, int64_t K, int y_is_colmajor, int out_dtype) {
+  return gemm_select_config(M, N, K, y_is_colmajor != 0, out_dtype, 148);
+}
+
+int hb200_fp8_gemm(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K, int64_t x_rs,
+                   int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs, int out_dtype, int cfg_id,
+                   void* workspace, size_t workspace_bytes, int device, void* stream) {
+  if (out_dtype != HB200_DT_FP16 && out_dtype != HB200_DT_BF16 && out_dtype != HB200_DT_FP32) {
+    return set_error(HB200_ERR_BAD_DTYPE, "fp8_gemm: out_dtype must be FP16, BF16 or FP32");
+  }
+  if (M < 1 || N < 1 || K < 1 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) {
+    return set_error(HB200_ERR_BAD_SHAPE, "fp8_gemm: M, N, K must be in [1, 2^31)");
+  }
+  if (K % 16 != 0) return set_error(HB200_ERR_BAD_SHAPE, "fp8_gemm: K must be a multiple of 16");
+  if (N % 8 != 0) return set_error(HB200_ERR_BAD_SHAPE, "fp8_gemm: N must be a multiple of 8");
+  if (x == nullptr || y == nullptr || out == nullptr) return set_error(HB200_ERR_ALIGN, "fp8_gemm: null pointer");
+  if (x_cs != 1) return set_error(HB200_ERR_BAD_STRIDE, "fp8_gemm: x must be row-major (column stride 1)");
+  if (x_rs < K || x_rs % 16 != 0) {
+    return set_error(HB200_ERR_BAD_STRIDE, "fp8_gemm: x row stride must be >= K and a multiple of 16");
+  }
+  bool y_colmajor;
+  int64_t ldb;
+  if (y_rs == 1 && (K == 1 || y_cs >= K)) {
+    y_colmajor = true;
+    ldb = y_cs;
+  } else if (y_cs == 1 && y_rs >= N) {
+    y_colmajor = false;
+    ldb = y_rs;
+    if (N % 16 != 0) return set_error(HB200_ERR_BAD_SHAPE, "fp8_gemm: row-major y needs N to be a multiple of 16");
+  } else {
+    return set_error(HB200_ERR_BAD_STRIDE, "fp8_gemm: y must be column-major (row stride 1) or row-major (column stride 1)");
+  }
+  if (ldb % 16 != 0) return set_error(HB200_ERR_BAD_STRIDE, "fp8_gemm: y leading stride must be a multiple of 16");
+  const int64_t out_elem = out_dtype == HB200_DT_FP32 ? 4 : 2;
+  if (out_rs < N || (out_rs * out_elem) % 16 != 0) {
+    return set_error(HB200_ERR_BAD_STRIDE, "fp8_gemm: out row stride must be >= N and give 16-byte aligned rows");
+  }
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out)) & 15u) {
+    return set_error(HB200_ERR_ALIGN, "fp8_gemm: x, y and out must be 16-byte aligned");
+  }
+  DeviceCtx* ctx = get_device_ctx(device);
+  if (ctx == nullptr) return ctx_error_code(device);
+  GemmArgs a;
+  a.x = x;
+  a.y = y;
+  a.out = out;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.lda = x_rs;
+  a.ldb = ldb;
+  a.y_colmajor = y_colmajor;
+  a.ldc = out_rs;
+  a.out_dtype = out_dtype;
+  a.cfg_id = cfg_id;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  a.device = device;
+  a.stream = static_cast<cudaStream_t>(stream);
+  DeviceGuard guard(device);
+  return launch_fp8_gemm(a, ctx);
+}
+
+int hb200_fp8_attention(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S, int64_t D,
+                        const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                        const int64_t out_strides[3], float scale_log2, int out_dtype, int cfg_id, int device,
+                        void* stream) {
+  if (out_dtype != HB200_DT_E4M3 && out_dtype != HB200_DT_BF16 && out_dtype != HB200_DT_FP32) {
+    return set_error(HB200_ERR_BAD_DTYPE, "fp8_attention: out_dtype must be E4M3, BF16 or FP32");
+  }
+  if (D != 64 && D != 128) return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: head_dim must be 64 or 128");
+  if (BH < 1 || S < 1 || BH > INT32_MAX || S > INT32_MAX) {
+    return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: batch*heads and seq must be in [1, 2^31)");
+  }
+  if (S % 16 != 0) return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: seq must be a multiple of 16");
+  if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || q_strides == nullptr ||
+      k_strides == nullptr || v_strides == nullptr || out_strides == nullptr) {
+    return set_error(HB200_ERR_ALIGN, "fp8_attention: null pointer");
+  }
+  if (q_strides[2] != 1 || k_strides[2] != 1 || out_strides[2] != 1) {
+    return set_error(HB200_ERR_BAD_STRIDE, "fp8_attention: q, k and out need a unit head_dim stride");
+  }
+  if (q_strides[1] % 16 != 0 || k_strides[1] % 16 != 0 || q_strides[0] % 16 != 0 || k_strides[0] % 16 != 0 ||
+      q_strides[1] < D || k_strides[1] < D) {
+    return set_error(HB200_ERR_BAD_STRIDE, "fp8_attention: q/k row and slice strides must be multiples of 16 and >= D");
+  }
+  if (!((v_strides[1] == 1 && v_strides[2] >= D) || (v_strides[2] == 1 && v_strides[1] >= S))) {
+    return set_error(HB200_ERR_BAD_STRIDE,
+                     "fp8_attention: v (logical [BH, D, S]) must have a unit stride along D or along S");
+  }
+  if (v_strides[0] % 16 != 0 || (v_strides[1] == 1 ? v_strides[2] : v_strides[1]) % 16 != 0) {
+    return set_error(HB200_ERR_BAD_STRIDE, "fp8_attention: v strides must be multiples of 16");
+  }
+  const int64_t out_elem = out_dtype == HB200_DT_FP32 ? 4 : (out_dtype == HB200_DT_BF16 ? 2 : 1);
+  if (out_strides[1] < D || (out_strides[1] * out_elem) % 16 != 0 || (out_strides[0] * out_elem) % 16 != 0) {
+    return set_error(HB200_ERR_BAD_STRIDE, "fp8_attention: out rows must be 16-byte aligned");
+  }
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(out)) & 15u) {
+    return set_error(HB200_ERR_ALIGN, "fp8_attention: q, k, v and out must be 16-byte aligned");
+  }
+  DeviceCtx* ctx = get_device_ctx(device);
+  if (ctx == nullptr) return ctx_error_code(device);
+  AttnArgs a;
+  a.q = q;
+  a.k = k;
+  a.v = v;
+  a.out = out;
+  a.BH = BH;
+  a.S = S;
+  a.D = D;
+  for (int i = 0; i < 3; ++i) {
+    a.q_strides[i] = q_strides[i];
+    a.k_strides[i] = k_strides[i];
+    a.v_strides[i] = v_strides[i];
+    a.out_strides[i] = out_strides[i];
+  }
+  a.scale_log2 = scale_log2;
+  a.out_dtype = out_dtype;
+  a.cfg_id = cfg_id;
+  a.device = device;
+  a.stream = static_cast<cudaStream_t>(stream);
+  DeviceGuard guard(device);
+  return launch_fp8_attention(a, ctx);
+}
+
+}  // extern "C"

@@ -1,0 +1,508 @@
+// FP8 attention forward (non-causal) for sm_100a with the numerics of pytorch-labs/helion's
+// examples/fp8_attention.py:54-105:
+//   s = (q k^T) * c            e4m3 x e4m3 -> fp32,  c = log2(e)/sqrt(D)
+//   m = running row max, p = exp2(s - m), l = l*alpha + rowsum(p)   (fp32, online softmax)
+//   acc = acc*alpha + e4m3(p) v                                     (P cast to e4m3 un-normalised)
+//   out = cast(acc / l)
+//
+// One CTA owns one (batch*head, 128-query-row) tile at a time and walks the keys in steps of 128;
+// CTAs are persistent, two per SM, so that one CTA's softmax overlaps the other's MMAs.
+//
+//   warp 0      TMA producer: Q tile, then K/V tiles through one ring of smem slots
+//   warp 1      MMA issuer (one thread): S = Q K^T into tensor memory, then O += P V with P read
+//               from shared memory; tcgen05.commit publishes S / frees slots / publishes O
+//   warp 2      tensor-memory allocation
+//   warps 4-7   softmax: each thread owns one query row: pulls its 128 scores out of tensor memory
+//               into registers (which frees S for the next Q K^T at once), row max, exp2, row sum,
+//               e4m3 P into 128B-swizzled smem, rescales O in tensor memory when the max moved,
+//               and writes the normalised output at the end of the tile
+//
+// V is accepted in both physical layouts of the reference's "[BH, D, S]" argument: D contiguous
+// (B operand of P V is MN-major) or S contiguous (K-major).
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+
+#include "common.cuh"
+#include "host.h"
+
+namespace hb {
+
+namespace {
+
+constexpr int ATT_BM = 128;  // query rows per tile (= UMMA M, one row per softmax thread)
+constexpr int ATT_BN = 128;  // keys per step
+constexpr int ATT_THREADS = 256;
+constexpr int ATT_SOFTMAX_THREADS = 128;
+constexpr int ATT_TMEM_COLS = 256;  // S: columns [0,128), O: columns [128, 128+D)
+constexpr int ATT_O_COL = 128;
+
+template <int D>
+struct AttnLayout {
+  static constexpr int KV_STAGES = (D == 64) ? 8 : 4;
+  static constexpr int TILE_BYTES = 128 * D;  // one Q, K or V tile
+  static constexpr int Q_OFFSET = 0;
+  static constexpr int P_OFFSET = TILE_BYTES;                 // 128 x 128 e4m3
+  static constexpr int KV_OFFSET = P_OFFSET + ATT_BM * ATT_BN;
+  static constexpr int BAR_OFFSET = KV_OFFSET + KV_STAGES * TILE_BYTES;
+  // q_full q_empty s_full s_free p_full pv_done drain kv_full[ST] kv_empty[ST]
+  static constexpr int NUM_BARS = 7 + 2 * KV_STAGES;
+  static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;
+  static constexpr int SMEM_BYTES = MISC_OFFSET + 16 + 1024;
+  static_assert(SMEM_BYTES <= 113 * 1024, "two CTAs must fit one SM");
+};
+
+__device__ __forceinline__ void reg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
+__device__ __forceinline__ void reg_inc_200() { asm volatile("setmaxnreg.inc.sync.aligned.u32 200;"); }
+
+template <int D, bool V_KMAJOR, int OUT_DT>
+__global__ void __launch_bounds__(ATT_THREADS, 2)
+fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, void* out, int BH, int S, int64_t out_stride_bh,
+                     int64_t out_stride_s, float scale_log2, uint32_t* status) {
+  using L = AttnLayout<D>;
+  constexpr int ST = L::KV_STAGES;
+  constexpr uint32_t SWZ_QK = (D == 128) ? SWZ_128B : SWZ_64B;  // rows of Q/K/V tiles are D bytes long
+  constexpr uint32_t SBO_QK = 8 * D;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* q_full = bars + 0;
+  uint64_t* q_empty = bars + 1;
+  uint64_t* s_full = bars + 2;
+  uint64_t* s_free = bars + 3;
+  uint64_t* p_full = bars + 4;
+  uint64_t* pv_done = bars + 5;
+  uint64_t* drain = bars + 6;
+  uint64_t* kv_full = bars + 7;
+  uint64_t* kv_empty = bars + 7 + ST;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFFSET + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (S + ATT_BM - 1) / ATT_BM;
+  const int n_steps = (S + ATT_BN - 1) / ATT_BN;
+  const int num_tiles = BH * m_tiles;
+  const WaitCtx wctx{abort_flag, status};
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(s_free, ATT_SOFTMAX_THREADS);
+    mbar_init(p_full, ATT_SOFTMAX_THREADS);
+    mbar_init(pv_done, 1);
+    mbar_init(drain, 1);
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, ATT_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4) {
+    reg_dec_56();
+    if (warp == 0) {
+      // ------------------------------- TMA producer ------------------------------------------
+      if (lane == 0) {
+        tma_prefetch_desc(&tmap_q);
+        tma_prefetch_desc(&tmap_k);
+        tma_prefetch_desc(&tmap_v);
+        uint32_t slot_it = 0;  // running K/V tile counter (ring position)
+        uint32_t tile_iter = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
+          const int bh = tile / m_tiles;
+          const int mt = tile - bh * m_tiles;
+          if (!mbar_wait(q_empty, (tile_iter & 1u) ^ 1u, wctx, SITE_ATTN_Q)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(q_full, L::TILE_BYTES);
+          tma_load_3d(smem + L::Q_OFFSET, &tmap_q, q_full, 0, mt * ATT_BM, bh);
+          for (int j = 0; j < n_steps && ok; ++j) {
+#pragma unroll
+            for (int kv = 0; kv < 2; ++kv, ++slot_it) {
+              const uint32_t s = slot_it % ST;
+              const uint32_t ph = (slot_it / ST) & 1u;
+              if (!mbar_wait(&kv_empty[s], ph ^ 1u, wctx, SITE_ATTN_KV_EMPTY)) {
+                ok = false;
+                break;
+              }
+              uint8_t* dst = smem + L::KV_OFFSET + s * L::TILE_BYTES;
+              mbar_arrive_expect_tx(&kv_full[s], L::TILE_BYTES);
+              if (kv == 0) {
+                tma_load_3d(dst, &tmap_k, &kv_full[s], 0, j * ATT_BN, bh);
+              } else if constexpr (V_KMAJOR) {
+                tma_load_3d(dst, &tmap_v, &kv_full[s], j * ATT_BN, 0, bh);  // [D rows, 128 keys]
+              } else {
+                tma_load_3d(dst, &tmap_v, &kv_full[s], 0, j * ATT_BN, bh);  // [128 keys, D]
+              }
+            }
+          }
+        }
+        if (!ok) {
+          mbar_drain(q_full, tile_iter & 1u);
+          const uint32_t back = slot_it < static_cast<uint32_t>(ST) ? slot_it : static_cast<uint32_t>(ST);
+          for (uint32_t i = slot_it - back; i < slot_it; ++i) mbar_drain(&kv_full[i % ST], (i / ST) & 1u);
+        }
+      }
+      __syncwarp();
+    } else if (warp == 1) {
+      // ------------------------------- MMA issuer --------------------------------------------
+      if (lane == 0) {
+        constexpr uint32_t idesc_qk = make_idesc_e4m3(ATT_BM, ATT_BN, false, false);
+        constexpr uint32_t idesc_pv = make_idesc_e4m3(ATT_BM, D, false, !V_KMAJOR);
+        const uint32_t q_addr = smem_u32(smem + L::Q_OFFSET);
+        const uint32_t p_addr = smem_u32(smem + L::P_OFFSET);
+        const uint32_t kv_addr = smem_u32(smem + L::KV_OFFSET);
+        const uint32_t t_s = tmem_base;
+        const uint32_t t_o = tmem_base + ATT_O_COL;
+        const uint64_t q_desc = make_smem_desc(q_addr, 16, SBO_QK, SWZ_QK);
+        const uint64_t p_desc = make_smem_desc(p_addr, 16, 1024, SWZ_128B);
+        uint32_t g = 0;        // running step counter: phases of s_full / s_free / p_full / pv_done
+        uint32_t slot_it = 0;  // ring position of the K tile of the step whose Q K^T is issued next
+        uint32_t tile_iter = 0;
+        bool ok = true;
+
+        // Q K^T of one step: waits for the K tile (and for S to be free), issues D/32 MMAs.
+        auto issue_qk = [&](uint32_t k_slot_it, uint32_t step_g, bool last_of_tile) -> bool {
+          const uint32_t s = k_slot_it % ST;
+          if (!mbar_wait(&kv_full[s], (k_slot_it / ST) & 1u, wctx, SITE_ATTN_K_FULL)) return false;
+          if (step_g > 0 && !mbar_wait(s_free, (step_g - 1u) & 1u, wctx, SITE_ATTN_S_FREE)) return false;
+          tc_fence_after_sync();
+          const uint64_t k_desc = make_smem_desc(kv_addr + s * L::TILE_BYTES, 16, SBO_QK, SWZ_QK);
+#pragma unroll
+          for (int k = 0; k < D / 32; ++k) {
+            umma_f8_ss(t_s, desc_advance(q_desc, k * 32), desc_advance(k_desc, k * 32), idesc_qk, k != 0 ? 1u : 0u);
+          }
+          umma_commit(&kv_empty[s]);
+          if (last_of_tile) umma_commit(q_empty);
+          umma_commit(s_full);
+          return true;
+        };
+
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
+          if (!mbar_wait(q_full, tile_iter & 1u, wctx, SITE_ATTN_Q)) {
+            ok = false;
+            break;
+          }
+          if (!issue_qk(slot_it, g, n_steps == 1)) {
+            ok = false;
+            break;
+          }
+          for (int j = 0; j < n_steps; ++j, ++g, slot_it += 2) {
+            if (j + 1 < n_steps) {
+              if (!issue_qk(slot_it + 2, g + 1, j + 2 == n_steps)) {
+                ok = false;
+                break;
+              }
+            }
+            // O (+)= P V
+            const uint32_t vs = (slot_it + 1) % ST;
+            if (!mbar_wait(&kv_full[vs], ((slot_it + 1) / ST) & 1u, wctx, SITE_ATTN_V_FULL) ||
+                !mbar_wait(p_full, g & 1u, wctx, SITE_ATTN_P_FULL)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t v_addr = kv_addr + vs * L::TILE_BYTES;
+            // V [keys, D] with D contiguous: MN-major B, one swizzle-wide block of N, 8 key rows per
+            // atom.  V [D, keys] with keys contiguous: K-major B with 128-byte rows.
+            const uint64_t v_desc = V_KMAJOR ? make_smem_desc(v_addr, 16, 1024, SWZ_128B)
+                                             : make_smem_desc(v_addr, SBO_QK, SBO_QK, SWZ_QK);
+#pragma unroll
+            for (int k = 0; k < ATT_BN / 32; ++k) {
+              const uint64_t pd = desc_advance(p_desc, k * 32);
+              const uint64_t vd = desc_advance(v_desc, V_KMAJOR ? k * 32 : k * 32 * D);
+              umma_f8_ss(t_o, pd, vd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(&kv_empty[vs]);
+            umma_commit(pv_done);
+          }
+        }
+        if (!ok) {
+          umma_commit(drain);
+          mbar_drain(drain, 0);
+        }
+      }
+      __syncwarp();
+    }
+  } else {
+    // --------------------------------- softmax / epilogue --------------------------------------
+    reg_inc_200();
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_sel;
+    const uint32_t t_o = tmem_base + ATT_O_COL + lane_sel;
+    // P tile, 128-byte rows, 16-byte chunks XOR-swizzled with (row % 8)
+    uint8_t* p_row = smem + L::P_OFFSET + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
+    const uint32_t p_xor = static_cast<uint32_t>(row_in_tile & 7);
+    uint32_t g = 0;
+    bool ok = true;
+
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int bh = tile / m_tiles;
+      const int mt = tile - bh * m_tiles;
+      float m_i = -INFINITY;
+      float l_i = 0.0f;
+      for (int j = 0; j < n_steps; ++j, ++g) {
+        ok = mbar_wait(s_full, g & 1u, wctx, SITE_ATTN_S_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        uint32_t s[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, s[c]);
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        mbar_arrive(s_free);  // S may be overwritten by the next Q K^T
+
+        const int valid = S - j * ATT_BN;  // keys of this step that exist
+        if (valid < ATT_BN) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (c * 32 + i >= valid) s[c][i] = __float_as_uint(-INFINITY);
+            }
+          }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(s[c][i]));
+            mx1 = fmaxf(mx1, __uint_as_float(s[c][i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(s[c][i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(s[c][i + 3]));
+          }
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        const float m_new = fmaxf(m_i, mx * scale_log2);
+        const float alpha = fast_exp2(m_i - m_new);
+        const float neg_m = -m_new;
+
+        // exp2, row sum (from the fp32 values), e4m3 pack
+        float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
+        uint32_t packed[32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][i]), scale_log2, neg_m));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), scale_log2, neg_m));
+            const float p2 = fast_exp2(fmaf(__uint_as_float(s[c][i + 2]), scale_log2, neg_m));
+            const float p3 = fast_exp2(fmaf(__uint_as_float(s[c][i + 3]), scale_log2, neg_m));
+            sum0 += p0;
+            sum1 += p1;
+            sum2 += p2;
+            sum3 += p3;
+            packed[c * 8 + i / 4] = pack_e4m3x4(p0, p1, p2, p3);
+          }
+        }
+        l_i = l_i * alpha + ((sum0 + sum1) + (sum2 + sum3));
+
+        // The previous P V must be complete before P (smem) is overwritten or O is rescaled.
+        if (g > 0) {
+          ok = mbar_wait(pv_done, (g - 1u) & 1u, wctx, SITE_ATTN_PV_DONE);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+        }
+        if (j > 0) {
+          const bool moved = m_new > m_i;
+          if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld_32x32b_x32(t_o + c * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st_32x32b_x32(t_o + c * 32, o);
+            }
+            tmem_wait_st();
+          }
+        }
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          *reinterpret_cast<uint4*>(p_row + ((static_cast<uint32_t>(ch) ^ p_xor) << 4)) =
+              make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(p_full);
+        m_i = m_new;
+      }
+      if (!ok) break;
+
+      // ---- epilogue of the tile: out = O / l --------------------------------------------------
+      ok = mbar_wait(pv_done, (g - 1u) & 1u, wctx, SITE_ATTN_O_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = mt * ATT_BM + row_in_tile;
+      const int64_t out_off = static_cast<int64_t>(bh) * out_stride_bh + static_cast<int64_t>(row) * out_stride_s;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(t_o + c * 32, o);
+        tmem_wait_ld();
+        if (row < S) {
+          if constexpr (OUT_DT == HB200_DT_E4M3) {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              w[i] = pack_e4m3x4(__fdiv_rn(__uint_as_float(o[4 * i]), l_i), __fdiv_rn(__uint_as_float(o[4 * i + 1]), l_i),
+                                 __fdiv_rn(__uint_as_float(o[4 * i + 2]), l_i),
+                                 __fdiv_rn(__uint_as_float(o[4 * i + 3]), l_i));
+            }
+            uint8_t* dst = reinterpret_cast<uint8_t*>(out) + out_off + c * 32;
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(dst + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+          } else if constexpr (OUT_DT == HB200_DT_BF16) {
+            uint32_t w[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              w[i] = pack_bf16x2(__fdiv_rn(__uint_as_float(o[2 * i]), l_i), __fdiv_rn(__uint_as_float(o[2 * i + 1]), l_i));
+            }
+            uint16_t* dst = reinterpret_cast<uint16_t*>(out) + out_off + c * 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            }
+          } else {
+            float* dst = reinterpret_cast<float*>(out) + out_off + c * 32;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float4 v;
+              v.x = __fdiv_rn(__uint_as_float(o[4 * i]), l_i);
+              v.y = __fdiv_rn(__uint_as_float(o[4 * i + 1]), l_i);
+              v.z = __fdiv_rn(__uint_as_float(o[4 * i + 2]), l_i);
+              v.w = __fdiv_rn(__uint_as_float(o[4 * i + 3]), l_i);
+              *reinterpret_cast<float4*>(dst + i * 4) = v;
+            }
+          }
+        }
+      }
+      // O is read; the next tile's first P V (which overwrites it) is ordered after this thread's
+      // next arrival on p_full.
+      tc_fence_before_sync();
+    }
+  }
+
+  // ------------------------------- teardown ------------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, ATT_TMEM_COLS);
+  }
+}
+
+struct AttnConfig {
+  const char* note;
+};
+const AttnConfig kAttnConfigs[] = {
+    {"128 query rows x 128 keys per step, P through shared memory, 2 persistent CTAs per SM"},
+};
+constexpr int kNumAttnConfigs = 1;
+
+template <int D, bool V_KMAJOR, int OUT_DT>
+int launch_attn_instance(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, const CUtensorMap& tk,
+                         const CUtensorMap& tv) {
+  using L = AttnLayout<D>;
+  auto kernel = fp8_attention_kernel<D, V_KMAJOR, OUT_DT>;
+  static bool attr_set[64] = {};
+  if (!attr_set[a.device]) {
+    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
+    attr_set[a.device] = true;
+  }
+  const int64_t m_tiles = (a.S + ATT_BM - 1) / ATT_BM;
+  const int64_t num_tiles = a.BH * m_tiles;
+  if (num_tiles > INT32_MAX) return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: too many tiles");
+  const int grid = static_cast<int>(std::min<int64_t>(num_tiles, 2 * ctx->num_sms));
+  kernel<<<grid, ATT_THREADS, L::SMEM_BYTES, a.stream>>>(tq, tk, tv, a.out, static_cast<int>(a.BH),
+                                                         static_cast<int>(a.S), a.out_strides[0], a.out_strides[1],
+                                                         a.scale_log2, ctx->status_dev);
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB200_OK;
+}
+
+template <int D, bool V_KMAJOR>
+int launch_attn_by_dtype(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, const CUtensorMap& tk,
+                         const CUtensorMap& tv) {
+  switch (a.out_dtype) {
+    case HB200_DT_E4M3:
+      return launch_attn_instance<D, V_KMAJOR, HB200_DT_E4M3>(a, ctx, tq, tk, tv);
+    case HB200_DT_BF16:
+      return launch_attn_instance<D, V_KMAJOR, HB200_DT_BF16>(a, ctx, tq, tk, tv);
+    case HB200_DT_FP32:
+      return launch_attn_instance<D, V_KMAJOR, HB200_DT_FP32>(a, ctx, tq, tk, tv);
+    default:
+      return set_error(HB200_ERR_BAD_DTYPE, "fp8_attention: unsupported out_dtype");
+  }
+}
+
+}  // namespace
+
+int attn_num_configs() { return kNumAttnConfigs; }
+
+int attn_describe_config(int cfg_id, char* buf, int buf_len) {
+  if (cfg_id < 0 || cfg_id >= kNumAttnConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_attention: no such config");
+  return std::snprintf(buf, buf_len, "attention cfg %d: %s", cfg_id, kAttnConfigs[cfg_id].note);
+}
+
+int launch_fp8_attention(const AttnArgs& a, DeviceCtx* ctx) {
+  if (a.cfg_id >= kNumAttnConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_attention: no such config");
+  const bool v_kmajor = a.v_strides[2] == 1 && a.v_strides[1] != 1;  // keys contiguous
+  const uint32_t d = static_cast<uint32_t>(a.D);
+  const CUtensorMapSwizzle swz_d = a.D == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(a.D), static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.BH)};
+    const uint32_t box[3] = {d, 128, 1};
+    const uint64_t qs[2] = {static_cast<uint64_t>(a.q_strides[1]), static_cast<uint64_t>(a.q_strides[0])};
+    rc = encode_tmap_u8(&tq, a.q, 3, dims, qs, box, swz_d);
+    if (rc != HB200_OK) return rc;
+    const uint64_t ks[2] = {static_cast<uint64_t>(a.k_strides[1]), static_cast<uint64_t>(a.k_strides[0])};
+    rc = encode_tmap_u8(&tk, a.k, 3, dims, ks, box, swz_d);
+    if (rc != HB200_OK) return rc;
+    if (!v_kmajor) {
+      // physical [BH, S, D]: logical strides {bh, d, s} = {v_strides[0], 1, v_strides[2]}
+      const uint64_t vs[2] = {static_cast<uint64_t>(a.v_strides[2]), static_cast<uint64_t>(a.v_strides[0])};
+      rc = encode_tmap_u8(&tv, a.v, 3, dims, vs, box, swz_d);
+      if (rc != HB200_OK) return rc;
+    } else {
+      const uint64_t vdims[3] = {static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.D), static_cast<uint64_t>(a.BH)};
+      const uint32_t vbox[3] = {128, d, 1};
+      const uint64_t vs[2] = {static_cast<uint64_t>(a.v_strides[1]), static_cast<uint64_t>(a.v_strides[0])};
+      rc = encode_tmap_u8(&tv, a.v, 3, vdims, vs, vbox, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc != HB200_OK) return rc;
+    }
+  }
+  if (a.D == 64) {
+    return v_kmajor ? launch_attn_by_dtype<64, true>(a, ctx, tq, tk, tv)
+                    : launch_attn_by_dtype<64, false>(a, ctx, tq, tk, tv);
+  }
+  return v_kmajor ? launch_attn_by_dtype<128, true>(a, ctx, tq, tk, tv)
+                  : launch_attn_by_dtype<128, false>(a, ctx, tq, tk, tv);
+}
+
+}  // namespace hb

@@ -1,0 +1,408 @@
+// FP8 (e4m3 x e4m3 -> fp32) GEMM for sm_100a: out[M,N] = cast(x[M,K] @ y[K,N]).
+//
+// Computes what examples/fp8_gemm.py:29-57 of pytorch-labs/helion computes (zero-initialised
+// fp32 accumulator, hl.dot over K tiles, cast on store), as one persistent, warp-specialised
+// kernel:
+//
+//   warp 0   TMA producer: x and y tiles -> STAGES-deep ring of 128B-swizzled smem buffers
+//   warp 1   MMA issuer: one thread issues tcgen05.mma kind::f8f6f4 (M=128, N=BN, K=32) into one
+//            of two fp32 accumulators in tensor memory; tcgen05.commit releases smem stages and
+//            publishes finished accumulators
+//   warps 2-5 epilogue: tcgen05.ld the finished accumulator (while the MMA warp already fills the
+//            other one), convert to fp16/bf16/fp32, store
+//
+// Tiles are walked in the L2-friendly grouped order (GROUP_M row blocks share their column
+// blocks), the grid is one CTA per SM.  y may be column-major (B operand K-major) or row-major
+// (B operand MN-major); both are fed straight from TMA without a transpose pass.
+#include <algorithm>
+#include <cstdio>
+
+#include "common.cuh"
+#include "host.h"
+
+namespace hb {
+
+namespace {
+
+constexpr int BM = 128;      // rows of one output tile = UMMA M
+constexpr int BK = 128;      // bytes (= e4m3 elements) of K per pipeline stage = one swizzle row
+constexpr int UMMA_K = 32;   // K of one kind::f8f6f4 instruction
+constexpr int NUM_THREADS = 192;
+constexpr int NUM_EPI_THREADS = 128;
+
+template <int BN, int STAGES>
+struct GemmLayout {
+  static constexpr int A_BYTES = BM * BK;
+  static constexpr int B_BYTES = BN * BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  // full[STAGES] empty[STAGES] acc_full[2] acc_empty[2] drain[1]
+  static constexpr int NUM_BARS = 2 * STAGES + 5;
+  static constexpr int BAR_OFFSET = RING_BYTES;
+  static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;  // tmem base (4 B) + abort flag (4 B)
+  static constexpr int SMEM_BYTES = MISC_OFFSET + 16 + 1024;     // + slack to align the ring to 1024 B
+  static constexpr int TMEM_COLS = 2 * BN;                       // two accumulators; power of two >= 32
+  static_assert(TMEM_COLS == 512 || TMEM_COLS == 256 || TMEM_COLS == 128 || TMEM_COLS == 64, "tmem");
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+};
+
+struct TileCoord {
+  int m_blk;
+  int n_blk;
+};
+
+// Grouped ("L2 swizzled") order: consecutive tile indices walk down GROUP_M row blocks before
+// moving to the next column block, so CTAs that run at the same time share x and y tiles in L2.
+__device__ __forceinline__ TileCoord tile_coord(int tile, int m_tiles, int n_tiles, int group_m) {
+  const int per_group = group_m * n_tiles;
+  const int group = tile / per_group;
+  const int first_m = group * group_m;
+  const int rows = min(m_tiles - first_m, group_m);
+  const int in_group = tile - group * per_group;
+  TileCoord c;
+  c.m_blk = first_m + in_group % rows;
+  c.n_blk = in_group / rows;
+  return c;
+}
+
+template <int OUT_DT>
+__device__ __forceinline__ void store_row_chunk(void* out, int64_t row_offset_elems, int col0, int N,
+                                                const uint32_t (&r)[32]) {
+  if constexpr (OUT_DT == HB200_DT_FP32) {
+    float* dst = reinterpret_cast<float*>(out) + row_offset_elems + col0;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      if (col0 + g * 4 + 4 <= N) {
+        *reinterpret_cast<uint4*>(dst + g * 4) = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+      }
+    }
+  } else {
+    uint16_t* dst = reinterpret_cast<uint16_t*>(out) + row_offset_elems + col0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (col0 + g * 8 + 8 <= N) {
+        uint32_t p[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = __uint_as_float(r[g * 8 + 2 * j]);
+          const float hi = __uint_as_float(r[g * 8 + 2 * j + 1]);
+          p[j] = (OUT_DT == HB200_DT_BF16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+        }
+        *reinterpret_cast<uint4*>(dst + g * 8) = make_uint4(p[0], p[1], p[2], p[3]);
+      }
+    }
+  }
+}
+
+template <int BN, int STAGES, bool B_MN_MAJOR, int OUT_DT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, void* out,
+                int M, int N, int K, int64_t ldc, int group_m, uint32_t* status) {
+  using L = GemmLayout<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* acc_full = bars + 2 * STAGES;
+  uint64_t* acc_empty = bars + 2 * STAGES + 2;
+  uint64_t* drain = bars + 2 * STAGES + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFFSET + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + BK - 1) / BK;
+  const WaitCtx wctx{abort_flag, status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], NUM_EPI_THREADS);
+    }
+    mbar_init(drain, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, L::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer --------------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, group_m);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u, wctx, SITE_GEMM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + s * L::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + L::A_BYTES;
+          mbar_arrive_expect_tx(&full[s], L::STAGE_BYTES);
+          tma_load_2d(a_dst, &tmap_a, &full[s], kb * BK, tc.m_blk * BM);
+          if constexpr (!B_MN_MAJOR) {
+            // y column-major: rows of the map are columns of y, K is contiguous.
+            tma_load_2d(b_dst, &tmap_b, &full[s], kb * BK, tc.n_blk * BN);
+          } else {
+            // y row-major: N is contiguous; one box = 128 K rows x 128 bytes of N.
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j) {
+              tma_load_2d(b_dst + j * (BK * 128), &tmap_b, &full[s], tc.n_blk * BN + j * 128, kb * BK);
+            }
+          }
+        }
+      }
+      if (!ok) {
+        // Abort path: let the copies that were issued land before the CTA exits.
+        const uint32_t back = it < static_cast<uint32_t>(STAGES) ? it : static_cast<uint32_t>(STAGES);
+        for (uint32_t j = it - back; j < it; ++j) mbar_drain(&full[j % STAGES], (j / STAGES) & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ----------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_e4m3(BM, BN, false, B_MN_MAJOR);
+      uint32_t it = 0;
+      uint32_t tile_iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1u;
+        const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1u, wctx, SITE_GEMM_ACC_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&full[s], ph, wctx, SITE_GEMM_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + L::A_BYTES;
+          // A: K-major, 128-byte rows, 8-row atoms 1024 B apart.
+          const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024, SWZ_128B);
+          // B K-major: same shape of atom.  B MN-major: 128 bytes of N contiguous, 8 K rows per
+          // atom (1024 B apart), consecutive 128-column blocks BK*128 bytes apart.
+          const uint64_t b_desc = B_MN_MAJOR ? make_smem_desc(b_addr, BK * 128, 1024, SWZ_128B)
+                                             : make_smem_desc(b_addr, 16, 1024, SWZ_128B);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t ad = desc_advance(a_desc, k * UMMA_K);
+            const uint64_t bd = desc_advance(b_desc, B_MN_MAJOR ? k * UMMA_K * 128 : k * UMMA_K);
+            umma_f8_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);  // smem stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+      }
+      if (!ok) {
+        umma_commit(drain);
+        mbar_drain(drain, 0);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- epilogue ------------------------------------------------
+    const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
+    uint32_t tile_iter = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
+      const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, group_m);
+      const uint32_t acc = tile_iter & 1u;
+      const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+      bool ok = mbar_wait(&acc_full[acc], acc_ph, wctx, SITE_GEMM_ACC_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = tc.m_blk * BM + quarter * 32 + lane;
+      const int64_t row_off = static_cast<int64_t>(row) * ldc;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 2
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c, r);
+        tmem_wait_ld();
+        const int col0 = tc.n_blk * BN + c;
+        if (row < M && col0 < N) store_row_chunk<OUT_DT>(out, row_off, col0, N, r);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  // ------------------------------- teardown ----------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, L::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// tile-config table
+// ------------------------------------------------------------------------------------------------
+struct GemmConfig {
+  int bn;
+  int stages;
+  int group_m;
+  const char* note;
+};
+
+const GemmConfig kGemmConfigs[] = {
+    {256, 4, 8, "128x256x128 tiles, 4 stages, group_m 8: large tensor-bound problems"},
+    {128, 6, 8, "128x128x128 tiles, 6 stages, group_m 8: mid-size problems, better wave fill"},
+    {64, 8, 8, "128x64x128 tiles, 8 stages, group_m 8: small N / many more tiles (column-major y only)"},
+    {256, 4, 16, "128x256x128 tiles, 4 stages, group_m 16"},
+    {256, 4, 4, "128x256x128 tiles, 4 stages, group_m 4"},
+    {128, 6, 16, "128x128x128 tiles, 6 stages, group_m 16"},
+};
+constexpr int kNumGemmConfigs = sizeof(kGemmConfigs) / sizeof(kGemmConfigs[0]);
+
+template <int BN, int STAGES, bool B_MN, int OUT_DT>
+int launch_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
+  using L = GemmLayout<BN, STAGES>;
+  auto kernel = fp8_gemm_kernel<BN, STAGES, B_MN, OUT_DT>;
+  static bool attr_set[64] = {};
+  if (!attr_set[a.device]) {
+    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
+    attr_set[a.device] = true;
+  }
+  const int m_tiles = static_cast<int>((a.M + BM - 1) / BM);
+  const int n_tiles = static_cast<int>((a.N + BN - 1) / BN);
+  const int64_t num_tiles = static_cast<int64_t>(m_tiles) * n_tiles;
+  const int grid = static_cast<int>(std::min<int64_t>(num_tiles, ctx->num_sms));
+  kernel<<<grid, NUM_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, a.out, static_cast<int>(a.M), static_cast<int>(a.N),
+                                                         static_cast<int>(a.K), a.ldc, group_m, ctx->status_dev);
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB200_OK;
+}
+
+template <int BN, int STAGES, bool B_MN>
+int launch_by_dtype(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
+  switch (a.out_dtype) {
+    case HB200_DT_FP16:
+      return launch_instance<BN, STAGES, B_MN, HB200_DT_FP16>(a, ctx, ta, tb, group_m);
+    case HB200_DT_BF16:
+      return launch_instance<BN, STAGES, B_MN, HB200_DT_BF16>(a, ctx, ta, tb, group_m);
+    case HB200_DT_FP32:
+      return launch_instance<BN, STAGES, B_MN, HB200_DT_FP32>(a, ctx, ta, tb, group_m);
+    default:
+      return set_error(HB200_ERR_BAD_DTYPE, "fp8_gemm: unsupported out_dtype");
+  }
+}
+
+}  // namespace
+
+int gemm_num_configs() { return kNumGemmConfigs; }
+
+int gemm_describe_config(int cfg_id, char* buf, int buf_len) {
+  if (cfg_id < 0 || cfg_id >= kNumGemmConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: no such config");
+  const GemmConfig& c = kGemmConfigs[cfg_id];
+  return std::snprintf(buf, buf_len, "gemm cfg %d: BM=128 BN=%d BK=128 stages=%d group_m=%d (%s)", cfg_id, c.bn,
+                       c.stages, c.group_m, c.note);
+}
+
+size_t gemm_workspace_bytes(int64_t, int64_t, int64_t, int, int) { return 0; }
+
+// Chooses the tile width that minimises (waves x tile width), i.e. the time of the persistent
+// schedule in units of 128-row MMA columns; ties go to the wider tile (less smem traffic per flop).
+int gemm_select_config(int64_t M, int64_t N, int64_t K, bool y_colmajor, int out_dtype, int num_sms) {
+  (void)K;
+  (void)out_dtype;
+  const int64_t m_tiles = (M + BM - 1) / BM;
+  int best = 0;
+  int64_t best_cost = -1;
+  const int candidates[3] = {0, 1, 2};
+  for (int idx : candidates) {
+    const GemmConfig& c = kGemmConfigs[idx];
+    if (!y_colmajor && c.bn < 128) continue;
+    const int64_t tiles = m_tiles * ((N + c.bn - 1) / c.bn);
+    const int64_t waves = (tiles + num_sms - 1) / num_sms;
+    const int64_t cost = waves * c.bn;
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = idx;
+    }
+  }
+  return best;
+}
+
+int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
+  int cfg_id = a.cfg_id;
+  if (cfg_id < 0) cfg_id = gemm_select_config(a.M, a.N, a.K, a.y_colmajor, a.out_dtype, ctx->num_sms);
+  if (cfg_id >= kNumGemmConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: no such config");
+  const GemmConfig& c = kGemmConfigs[cfg_id];
+  if (!a.y_colmajor && c.bn < 128) {
+    return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: this config supports column-major y only");
+  }
+
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(a.lda)};
+    const uint32_t box[2] = {BK, BM};
+    int rc = encode_tmap_u8(&ta, a.x, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB200_OK) return rc;
+  }
+  if (a.y_colmajor) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.N)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(a.ldb)};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(c.bn)};
+    int rc = encode_tmap_u8(&tb, a.y, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB200_OK) return rc;
+  } else {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(a.ldb)};
+    const uint32_t box[2] = {128, BK};
+    int rc = encode_tmap_u8(&tb, a.y, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB200_OK) return rc;
+  }
+
+  if (a.y_colmajor) {
+    switch (c.bn) {
+      case 256:
+        return launch_by_dtype<256, 4, false>(a, ctx, ta, tb, c.group_m);
+      case 128:
+        return launch_by_dtype<128, 6, false>(a, ctx, ta, tb, c.group_m);
+      case 64:
+        return launch_by_dtype<64, 8, false>(a, ctx, ta, tb, c.group_m);
+    }
+  } else {
+    switch (c.bn) {
+      case 256:
+        return launch_by_dtype<256, 4, true>(a, ctx, ta, tb, c.group_m);
+      case 128:
+        return launch_by_dtype<128, 6, true>(a, ctx, ta, tb, c.group_m);
+    }
+  }
+  return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: config has no kernel instance");
+}
+
+}  // namespace hb

@@ -1,0 +1,110 @@
+// Host-side plumbing shared by the launchers: per-device context, error text, tensor-map
+// encoding.  Nothing here is visible outside the shared library.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/helion_b200.h"
+
+namespace hb {
+
+struct DeviceCtx {
+  bool initialised = false;
+  int init_error = 0;         // HB200_ERR_* if initialisation failed
+  int num_sms = 0;
+  int cc_major = 0;
+  int cc_minor = 0;
+  uint32_t* status_host = nullptr;  // mapped pinned word written by kernels whose waits ran out
+  uint32_t* status_dev = nullptr;   // device-side alias of status_host
+};
+
+// Lazily initialised, mutex-protected; returns nullptr (and sets the error text) on failure.
+DeviceCtx* get_device_ctx(int device);
+
+// Error code to return when get_device_ctx() gave nullptr.
+int device_init_error(int device);
+
+int set_error(int code, const std::string& text);
+const char* last_error_text();
+
+#define HB_CUDA_CHECK(expr)                                                                         \
+  do {                                                                                              \
+    cudaError_t _e = (expr);                                                                        \
+    if (_e != cudaSuccess) {                                                                        \
+      return ::hb::set_error(HB200_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e)); \
+    }                                                                                               \
+  } while (0)
+
+// Switches the current device for the duration of a launch and restores it afterwards.
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) == cudaSuccess && prev != device) {
+      switched = cudaSetDevice(device) == cudaSuccess;
+    }
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+// Encode a tiled tensor map over bytes.  dims/strides innermost first; strides[i] is the byte
+// stride of dimension i+1 (dimension 0 is contiguous).  Returns HB200_OK or an error code.
+int encode_tmap_u8(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                   const uint32_t* box, CUtensorMapSwizzle swizzle);
+
+// Same for 2- and 4-byte elements (used by the TMA-store epilogues).
+int encode_tmap(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, int rank, const uint64_t* dims,
+                const uint64_t* strides, const uint32_t* box, CUtensorMapSwizzle swizzle);
+
+// ---- launchers (one per .cu file) -----------------------------------------------------------
+struct GemmArgs {
+  const void* x;
+  const void* y;
+  void* out;
+  int64_t M, N, K;
+  int64_t lda;       // x row stride (elements)
+  int64_t ldb;       // y leading stride: column stride if column-major, row stride if row-major
+  bool y_colmajor;
+  int64_t ldc;       // out row stride (elements)
+  int out_dtype;
+  int cfg_id;
+  void* workspace;
+  size_t workspace_bytes;
+  int device;
+  cudaStream_t stream;
+};
+
+int launch_fp8_gemm(const GemmArgs& args, DeviceCtx* ctx);
+int gemm_num_configs();
+int gemm_describe_config(int cfg_id, char* buf, int buf_len);
+int gemm_select_config(int64_t M, int64_t N, int64_t K, bool y_colmajor, int out_dtype, int num_sms);
+size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int cfg_id);
+
+struct AttnArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  int64_t BH, S, D;
+  int64_t q_strides[3];
+  int64_t k_strides[3];
+  int64_t v_strides[3];    // logical [BH, D, S]
+  int64_t out_strides[3];  // [BH, S, D]
+  float scale_log2;
+  int out_dtype;
+  int cfg_id;
+  int device;
+  cudaStream_t stream;
+};
+
+int launch_fp8_attention(const AttnArgs& args, DeviceCtx* ctx);
+int attn_num_configs();
+int attn_describe_config(int cfg_id, char* buf, int buf_len);
+
+}  // namespace hb

@@ -1,0 +1,161 @@
+"""Host-side operators: torch tensors in, one C-ABI launch, torch tensor out.
+
+These functions do what the generated host functions of the reference do around their Triton
+launch (allocate the output with ``torch.empty`` on the inputs' device, launch on the current
+stream, return the output; pytorch-labs/helion ``examples/fp8_gemm.py:42-57``,
+``examples/fp8_attention.py:43-106``).  torch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_OUT_DT = {
+    torch.float16: _lib.DT_FP16,
+    torch.bfloat16: _lib.DT_BF16,
+    torch.float32: _lib.DT_FP32,
+    torch.float8_e4m3fn: _lib.DT_E4M3,
+}
+
+
+def _require_cuda(*tensors: torch.Tensor) -> int:
+    dev = tensors[0].device
+    if dev.type != "cuda":
+        raise RuntimeError(
+            f"helion_b200 runs on CUDA (sm_100a) tensors only, got a tensor on {dev}; there is no CPU fallback"
+        )
+    for t in tensors[1:]:
+        if t.device != dev:
+            raise RuntimeError(f"all tensors must be on the same device, got {dev} and {t.device}")
+    return dev.index if dev.index is not None else torch.cuda.current_device()
+
+
+def _stream_ptr(device_index: int) -> int:
+    return torch.cuda.current_stream(device_index).cuda_stream
+
+
+def fp8_gemm(
+    x: torch.Tensor,
+    y: torch.Tensor,
+    *,
+    out_dtype: torch.dtype = torch.float16,
+    config: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """``out = (x @ y).to(out_dtype)`` for float8_e4m3fn ``x [M,K]`` and ``y [K,N]``, fp32 accumulation.
+
+    Same contract as the reference's ``fp8_gemm(x, y)`` (examples/fp8_gemm.py:29-57): fp16 output by
+    default.  ``y`` may be row-major or column-major (a transposed view); ``x`` must be row-major.
+    ``out_dtype`` (fp16 / bf16 / fp32), ``config`` (tile-config id, None = table choice) and ``out``
+    are keyword-only extensions.
+    """
+    if x.dtype != torch.float8_e4m3fn or y.dtype != torch.float8_e4m3fn:
+        raise TypeError(f"fp8_gemm expects float8_e4m3fn inputs, got {x.dtype} and {y.dtype}")
+    if x.dim() != 2 or y.dim() != 2:
+        raise ValueError(f"fp8_gemm expects 2-D inputs, got {tuple(x.shape)} and {tuple(y.shape)}")
+    m, k = x.shape
+    k2, n = y.shape
+    assert k == k2, f"size mismatch {k} != {k2}"  # same check and text as examples/fp8_gemm.py:44
+    if out_dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise TypeError(f"fp8_gemm out_dtype must be float16, bfloat16 or float32, got {out_dtype}")
+    dev = _require_cuda(x, y)
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    if y.stride(0) != 1 and y.stride(1) != 1:
+        y = y.contiguous()
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    else:
+        if out.dtype != out_dtype or tuple(out.shape) != (m, n) or out.stride(1) != 1 or out.device != x.device:
+            raise ValueError("fp8_gemm: `out` must be a row-major [M, N] tensor of out_dtype on the inputs' device")
+    if m == 0 or n == 0:
+        return out
+    if k == 0:
+        return out.zero_()
+    lib = _lib.load()
+    code = lib.hb200_fp8_gemm(
+        x.data_ptr(), y.data_ptr(), out.data_ptr(), m, n, k,
+        x.stride(0), x.stride(1), y.stride(0), y.stride(1), out.stride(0),
+        _OUT_DT[out_dtype], -1 if config is None else int(config),
+        None, 0, dev, _stream_ptr(dev),
+    )
+    _lib.raise_for(code, "fp8_gemm")
+    return out
+
+
+def fp8_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    batch: int,
+    heads: int,
+    *,
+    out_dtype: torch.dtype = torch.float8_e4m3fn,
+    config: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Non-causal FP8 attention forward with the reference's numerics.
+
+    Same contract as the reference's ``fp8_attention_kernel(q, k, v, batch, heads)``
+    (examples/fp8_attention.py:22-106): ``q``, ``k`` are ``[batch*heads, seq, dim]`` e4m3, ``v`` is
+    the "pre-transposed" ``[batch*heads, dim, seq]`` e4m3 tensor (either physical layout), the
+    result is ``[batch, heads, seq, dim]`` e4m3.  ``out_dtype`` (e4m3 / bf16 / fp32), ``config`` and
+    ``out`` are keyword-only extensions.
+    """
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if t.dtype != torch.float8_e4m3fn:
+            raise TypeError(f"fp8_attention expects float8_e4m3fn inputs, {name} is {t.dtype}")
+        if t.dim() != 3:
+            raise ValueError(f"fp8_attention expects 3-D inputs, {name} has shape {tuple(t.shape)}")
+    bh, s, d = q.shape
+    if tuple(k.shape) != (bh, s, d) or tuple(v.shape) != (bh, d, s):
+        raise ValueError(
+            f"fp8_attention shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)} "
+            "(expected [BH,S,D], [BH,S,D], [BH,D,S])"
+        )
+    if bh != batch * heads:
+        raise ValueError(f"fp8_attention: q.size(0)={bh} != batch*heads={batch * heads}")
+    if out_dtype not in (torch.float8_e4m3fn, torch.bfloat16, torch.float32):
+        raise TypeError(f"fp8_attention out_dtype must be float8_e4m3fn, bfloat16 or float32, got {out_dtype}")
+    dev = _require_cuda(q, k, v)
+    if q.stride(2) != 1:
+        q = q.contiguous()
+    if k.stride(2) != 1:
+        k = k.contiguous()
+    if v.stride(1) != 1 and v.stride(2) != 1:
+        v = v.contiguous()
+    if out is None:
+        out = torch.empty((batch, heads, s, d), dtype=out_dtype, device=q.device)
+    elif out.dtype != out_dtype or tuple(out.shape) != (batch, heads, s, d) or not out.is_contiguous():
+        raise ValueError("fp8_attention: `out` must be a contiguous [batch, heads, seq, dim] tensor of out_dtype")
+    if bh == 0 or s == 0:
+        return out
+    attention_into(q, k, v, out.view(bh, s, d), config=config)
+    return out
+
+
+def attention_into(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out3: torch.Tensor, *, config: Optional[int] = None
+) -> None:
+    """Launch the attention kernel on ``[BH,S,D]`` / ``[BH,D,S]`` tensors, writing ``out3 [BH,S,D]``.
+
+    The batch*head slices are independent, so a shard of them (a slice along dim 0 of every
+    tensor) is a valid call; the multi-GPU driver uses exactly that.
+    """
+    bh, s, d = q.shape
+    dev = _require_cuda(q, k, v, out3)
+    # The kernel scales by log2(e)/sqrt(D) and uses exp2, like examples/fp8_attention.py:50-52.
+    scale_log2 = (1.0 / math.sqrt(float(d))) * 1.44269504
+    arr = ctypes.c_int64 * 3
+    lib = _lib.load()
+    code = lib.hb200_fp8_attention(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), out3.data_ptr(), bh, s, d,
+        arr(*q.stride()), arr(*k.stride()), arr(*v.stride()), arr(*out3.stride()),
+        scale_log2, _OUT_DT[out3.dtype], -1 if config is None else int(config), dev, _stream_ptr(dev),
+    )
+    _lib.raise_for(code, "fp8_attention")

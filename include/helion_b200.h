@@ -1,0 +1,124 @@
+/* helion_b200.h -- C ABI of the B200 (sm_100a) FP8 GEMM / FP8 attention library.
+ *
+ * The library replaces, for two kernels of pytorch-labs/helion, everything below the Python
+ * call `fp8_gemm(x, y)` / `fp8_attention_kernel(q, k, v, batch, heads)`: Helion's generated
+ * Triton kernel and its launcher (helion/runtime/__init__.py:55-65, `default_launcher`, which is
+ * what the generated host function calls, test/test_examples.expected:836-840 and :786-790).
+ * Helion has no FFI of its own (it is pure Python), so these entry points are the boundary a
+ * maintainer binds with ctypes from the two example modules.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; all pointers are DEVICE pointers unless stated otherwise;
+ *   - every launch is asynchronous on the given stream (a `cudaStream_t`, passed as void*) and
+ *     performs no allocation and no synchronisation once the device has been initialised
+ *     (first call on a device creates a small per-device context);
+ *   - return value 0 = launched, negative = HB200_ERR_*; `hb200_last_error()` gives the text;
+ *   - strides are in ELEMENTS;
+ *   - fp8 means float8_e4m3fn bit patterns (1 byte per element).
+ */
+#ifndef HELION_B200_H
+#define HELION_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HB200_VERSION 1
+
+#if defined(__GNUC__)
+#define HB200_API __attribute__((visibility("default")))
+#else
+#define HB200_API
+#endif
+
+/* error codes */
+#define HB200_OK 0
+#define HB200_ERR_BAD_DTYPE (-1)
+#define HB200_ERR_BAD_SHAPE (-2)
+#define HB200_ERR_BAD_STRIDE (-3)
+#define HB200_ERR_ALIGN (-4)
+#define HB200_ERR_UNSUPPORTED_ARCH (-5)
+#define HB200_ERR_CUDA (-6)
+#define HB200_ERR_TIMEOUT (-7)
+#define HB200_ERR_BAD_CONFIG (-8)
+#define HB200_ERR_WORKSPACE (-9)
+
+/* output element types */
+#define HB200_DT_FP16 0
+#define HB200_DT_BF16 1
+#define HB200_DT_FP32 2
+#define HB200_DT_E4M3 3
+
+/* operations (for the tile-config queries) */
+#define HB200_OP_GEMM 0
+#define HB200_OP_ATTENTION 1
+
+/* out[M,N] = cast(x[M,K] @ y[K,N]), e4m3 operands, fp32 accumulation.
+ * Replaces the device kernel of examples/fp8_gemm.py:29-57 (`fp8_gemm`) and its launch.
+ *   x: fp8, x_cs must be 1 (row-major), x_rs % 16 == 0, pointer 16-byte aligned.
+ *   y: fp8, either column-major (y_rs == 1, y_cs % 16 == 0) or row-major (y_cs == 1,
+ *      y_rs % 16 == 0), pointer 16-byte aligned.
+ *   out: row-major, out_rs in elements, rows 16-byte aligned; out_dtype one of FP16/BF16/FP32
+ *      (FP16 is what the reference produces).
+ *   K % 16 == 0, N % 8 == 0, M >= 1.
+ *   cfg_id: index into the tile-config table, or -1 to let the library choose from the table.
+ *   workspace: scratch for split-K configurations (fp32 partial sums), may be NULL when
+ *      hb200_fp8_gemm_workspace_bytes() returns 0 for the configuration.
+ */
+HB200_API int hb200_fp8_gemm(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K, int64_t x_rs,
+                   int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs, int out_dtype, int cfg_id,
+                   void* workspace, size_t workspace_bytes, int device, void* stream);
+
+/* Bytes of workspace hb200_fp8_gemm needs for this problem and configuration (0 for most). */
+HB200_API size_t hb200_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int cfg_id);
+
+/* The configuration the library would choose for this problem when cfg_id == -1. */
+HB200_API int hb200_fp8_gemm_select_config(int64_t M, int64_t N, int64_t K, int y_is_colmajor, int out_dtype);
+
+/* out[bh, s, :] = cast( softmax(q k^T * scale) v ), per batch*head slice, non-causal, with the
+ * reference's numerics: scores and softmax in fp32 with exp2, P cast to e4m3 UN-normalised
+ * before P@V, the row sum taken from the fp32 P, division by the row sum at the end.
+ * Replaces the device kernel of examples/fp8_attention.py:22-106 (`fp8_attention_kernel`).
+ *   q, k: fp8 [BH, S, D], innermost stride 1, row stride D... given as {bh, s, d} strides.
+ *   v: fp8 with LOGICAL shape [BH, D, S] (the reference's "pre-transposed" argument); strides
+ *      {bh, d, s}.  Both physical layouts occur: stride_d == 1 (what
+ *      preprocess_fp8_attention_inputs really produces, examples/fp8_attention.py:127-132) and
+ *      stride_s == 1 (a genuinely contiguous [BH, D, S]).
+ *   out: [BH, S, D] with strides {bh, s, d}, d stride 1; FP8 (reference), or BF16 / FP32.
+ *   D in {64, 128}; S >= 1 with S % 16 == 0; scale_log2 = log2(e)/sqrt(D) for the reference's
+ *   scale (examples/fp8_attention.py:50-52).
+ */
+HB200_API int hb200_fp8_attention(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S, int64_t D,
+                        const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                        const int64_t out_strides[3], float scale_log2, int out_dtype, int cfg_id, int device,
+                        void* stream);
+
+/* Tile-config table introspection (the table replaces Helion's autotuner,
+ * helion/autotuner/differential_evolution.py:20-101). */
+HB200_API int hb200_num_configs(int op);
+/* Writes a NUL-terminated description into buf (at most buf_len bytes); returns its length. */
+HB200_API int hb200_describe_config(int op, int cfg_id, char* buf, int buf_len);
+
+/* Device-side status word of the bounded waits: returns 0 if no wait ran out on this device
+ * since the last reset, else HB200_ERR_TIMEOUT with *site = (wait site << 16) | block index.
+ * Reads mapped host memory; does not synchronise.  hb200_reset_status clears it. */
+HB200_API int hb200_read_status(int device, uint32_t* site);
+HB200_API int hb200_reset_status(int device);
+
+/* Number of SMs the persistent kernels size their grids with (cudaDevAttrMultiProcessorCount;
+ * the role of helion/runtime/__init__.py:41-52 `get_num_sm`). */
+HB200_API int hb200_num_sms(int device);
+
+/* Thread-local text of the last error returned on this thread. */
+HB200_API const char* hb200_last_error(void);
+
+HB200_API int hb200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* HELION_B200_H */
