@@ -1,0 +1,456 @@
+"""Benchmark of the FP8 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A "step" is one FP8 GEMM M=N=K=8192 (e4m3 operands from a seeded N(0,1) draw, y column-major,
+fp32 accumulation, bf16 output) per GPU.  With N GPUs every rank owns one 8192-row block of a
+global [8192*N, 8192] x and a replica of y (row sharding, no collective on the compute path), so
+per-GPU work is fixed ("weak" scaling) and `value` is the aggregate TFLOP/s of all ranks.
+
+Printed (rank 0, one JSON line): the device-timed throughput (`value`), the same metric end to
+end through the public API with host buffers (`e2e`), the roofline of the GEMM kernel, the CPU
+baseline (the oracle timed on a bounded sample), clocks sampled during the timed region, and --
+as additional objects measured in the same run -- FP8 attention (B4 H48 S1024 D64 and
+B8 H32 S4096 D128) and the LLM-MLP GEMM shapes.
+
+`--impl reference` times the reference's CPU path instead (the numpy restatement of Helion's
+ref-eager arithmetic in oracle/, since the reference itself is Python that does not travel to the
+benchmark machine) on a bounded row block of the same workload, on rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+M = N = K = 8192
+GEMM_FLOPS = 2.0 * M * N * K
+NOMINAL_FP8_TFLOPS = 4500.0
+NOMINAL_HBM_GBS = 8000.0
+METRIC = "FP8 GEMM TFLOP/s (M=N=K=8192, e4m3 x e4m3, fp32 accumulate, bf16 out)"
+
+
+def load_peaks():
+    """Measured peaks of this pool (driver-written file) or the documented fallback."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        p = json.loads(path.read_text())
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs (read-only)."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # the median over the busiest half of the samples = the clock under load
+        busy = sorted(zip(power, sm))[len(sm) // 2:] if sm else []
+        return {
+            "sm_mhz": statistics.median(s for _, s in busy) if busy else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "power_w_max": max(power) if power else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+def time_steps(fn, steps, warmup, flush, torch, stream=None):
+    """Per-step CUDA-event times (ms) on the current stream; L2 is flushed before every step."""
+    for _ in range(warmup):
+        flush()
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(steps):
+        flush()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        times.append(a.elapsed_time(b))
+    return times
+
+
+CPU_SAMPLE_ROWS = 128
+
+
+def cpu_reference_inputs(rows: int):
+    """The first `rows` rows of the benchmark's x and its full y, as e4m3 bit patterns."""
+    from oracle import fp8_oracle as o
+
+    x, y = o.gemm_inputs(M, N, K, seed=1)
+    return o.torch_fp8_to_bits(x[:rows]), o.torch_fp8_to_bits(y)
+
+
+def cpu_reference_pass(xb, yb):
+    """One pass of the oracle's GEMM (dequantise, fp32 matmul, round to bf16); returns seconds."""
+    import numpy as np
+
+    from oracle import fp8_oracle as o
+
+    t0 = time.perf_counter()
+    out = o.fp8_gemm(xb, yb, "bf16")
+    dt = time.perf_counter() - t0
+    assert np.isfinite(out).all()
+    return dt
+
+
+def aten_scaled_mm_cpu_gflops():
+    """The call the reference's ref-eager mode really makes on CPU tensors (ATen _scaled_mm,
+    helion/language/matmul_ops.py:235-242), timed on a 256^3 problem."""
+    import torch
+
+    from oracle import fp8_oracle as o
+
+    x, y = o.gemm_inputs(256, 256, 256, seed=0)
+    one = torch.tensor(1.0)
+    try:
+        torch._scaled_mm(x, y, one, one, use_fast_accum=False, out_dtype=torch.float32)
+        t0 = time.perf_counter()
+        torch._scaled_mm(x, y, one, one, use_fast_accum=False, out_dtype=torch.float32)
+        return 2.0 * 256 ** 3 / (time.perf_counter() - t0) / 1e9
+    except Exception:  # not every torch build has the CPU kernel
+        return None
+
+
+def run_reference(args, rank: int) -> None:
+    if rank != 0:
+        return
+    import torch
+
+    rows = CPU_SAMPLE_ROWS
+    threads = torch.get_num_threads()
+    xb, yb = cpu_reference_inputs(rows)
+    for _ in range(args.warmup):
+        cpu_reference_pass(xb, yb)
+    times = [cpu_reference_pass(xb, yb) for _ in range(args.steps)]
+    sec = statistics.mean(times)
+    tflops = 2.0 * rows * N * K / sec / 1e12
+    sample = f"rows 0..{rows - 1} of x against the full y ({rows}x{N}x{K}) per step"
+    line = {
+        "impl": "reference",
+        "metric": METRIC,
+        "value": tflops,
+        "unit": "TFLOP/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": sec * 1e3,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "e4m3 x e4m3 -> fp32",
+        "data": "synthetic",
+        "config": {"workload": "fp8_gemm M=N=K=8192, y column-major, bf16 out", "sample": sample},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample,
+                         "aten_scaled_mm_cpu_gflops_256": aten_scaled_mm_cpu_gflops()},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the attention / MLP-shape sections")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import helion_b200 as hb
+    from helion_b200 import _lib
+    from oracle import fp8_oracle as o  # input generators + the CPU baseline leg only
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    warmup = max(args.warmup, 3)
+    peaks = load_peaks()
+    fp8_peak = 2.0 * peaks["bf16_tflops"]  # dense FP8 issues at twice the bf16 rate
+
+    # ---- workload: this rank's 8192-row block of x, replicated column-major y ------------------
+    y_host = o.gemm_inputs(M, N, K, seed=1)[1]  # the same y on every rank
+    x_host = o.gemm_inputs(M, N, K, seed=1 + rank)[0]
+    x_pin = x_host.view(torch.uint8).pin_memory()
+    y_pin = y_host.t().contiguous().view(torch.uint8).pin_memory()  # [N, K] bytes = column-major y
+    out_pin = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    x = x_pin.to(dev, non_blocking=True).view(torch.float8_e4m3fn)
+    y = y_pin.to(dev, non_blocking=True).view(torch.float8_e4m3fn).t()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+
+    def flush():
+        flush_buf.zero_()
+
+    def step():
+        hb.fp8_gemm(x, y, out_dtype=torch.bfloat16, out=out)
+
+    _lib.reset_status(local_rank)
+
+    # ---- device-timed region --------------------------------------------------------------------
+    for _ in range(warmup):
+        flush()
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    torch.cuda.synchronize()
+    times = time_steps(step, args.steps, 0, flush, torch)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    total_ms = sum(times)
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms_max = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check_status(local_rank)
+    ms_per_step = total_ms_max / args.steps
+    value = world * GEMM_FLOPS / (ms_per_step * 1e-3) / 1e12
+    kernel_ms = statistics.mean(times)  # one launch per step: the step time IS the kernel time
+    achieved = GEMM_FLOPS / (kernel_ms * 1e-3) / 1e12
+
+    # ---- end to end: host buffers in, host buffer out, copies inside the timed region ----------
+    def e2e_step():
+        xd = x_pin.to(dev, non_blocking=True).view(torch.float8_e4m3fn)
+        yd = y_pin.to(dev, non_blocking=True).view(torch.float8_e4m3fn).t()
+        res = hb.fp8_gemm(xd, yd, out_dtype=torch.bfloat16)
+        out_pin.copy_(res, non_blocking=True)
+
+    e2e_steps = min(args.steps, 20)
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a = torch.cuda.Event(enable_timing=True)
+    b = torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    b.record()
+    torch.cuda.synchronize()
+    e2e_ms = torch.tensor([a.elapsed_time(b) / e2e_steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.barrier()
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = world * GEMM_FLOPS / (float(e2e_ms.item()) * 1e-3) / 1e12
+    got = out_pin[:64].float().numpy()
+
+    line = None
+    if rank == 0:
+        # sanity of the e2e result against the oracle on a row block (not timed)
+        want = o.fp8_gemm(o.torch_fp8_to_bits(x_host[:64]), o.torch_fp8_to_bits(y_host), "bf16")
+        import numpy as np
+
+        np.testing.assert_allclose(got, want, rtol=2e-2, atol=2e-2)
+
+        extras = {}
+        if not args.no_extras:
+            extras = run_extras(hb, _lib, o, torch, dev, flush, fp8_peak, peaks)
+        cpu_sec = cpu_tflops = None
+        if world == 1:
+            xb, yb = cpu_reference_inputs(CPU_SAMPLE_ROWS)
+            cpu_sec = min(cpu_reference_pass(xb, yb) for _ in range(5))
+            cpu_tflops = 2.0 * CPU_SAMPLE_ROWS * N * K / cpu_sec / 1e12
+        line = {
+            "metric": METRIC,
+            "value": value,
+            "unit": "TFLOP/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": warmup,
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "e4m3 x e4m3 -> fp32",
+            "data": "synthetic",
+            "config": {
+                "workload": "fp8_gemm M=N=K=8192 per GPU, y column-major, bf16 out (BASELINE config 2)",
+                "global_M": M * world,
+                "sharding": "rows of x per rank, y replicated, no collective",
+                "l2": "512 MiB buffer written before every timed step; inputs+output (268 MB) also exceed L2",
+                "tile_config": _lib.describe_config(_lib.OP_GEMM, _lib.load().hb200_fp8_gemm_select_config(M, N, K, 1, 1)),
+            },
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+            "e2e": {
+                "value": e2e_value,
+                "unit": "TFLOP/s",
+                "h2d_bytes_per_step": int(x_pin.numel() + y_pin.numel()),
+                "d2h_bytes_per_step": int(out_pin.numel() * 2),
+                "steps": e2e_steps,
+                "ms_per_step": float(e2e_ms.item()),
+            },
+            "roofline": {
+                "bound": "tensor",
+                "achieved": achieved,
+                "peak": fp8_peak,
+                "unit": "TFLOP/s",
+                "frac": achieved / fp8_peak,
+                "peak_source": f"2 x bf16_tflops ({peaks['bf16_tflops']}) of {peaks['source']}; dense FP8 issues at twice the bf16 rate",
+                "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
+                "algorithmic_flops_per_launch": GEMM_FLOPS,
+                "kernel_ms": kernel_ms,
+                "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                "algorithmic_bytes_per_launch": M * K + K * N + 2 * M * N,
+            },
+        }
+        if world == 1:
+            line["cpu_baseline"] = {
+                "value": cpu_tflops,
+                "unit": "TFLOP/s",
+                "cores": torch.get_num_threads(),
+                "kind": "port",
+                "sample": f"rows 0..{CPU_SAMPLE_ROWS - 1} of x against the full y ({CPU_SAMPLE_ROWS}x{N}x{K}), best of 5, {cpu_sec:.2f} s per pass",
+                "aten_scaled_mm_cpu_gflops_256": aten_scaled_mm_cpu_gflops(),
+            }
+        line.update(extras)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch from the committed ncu summary
+# (profiles/); None until a capture exists.
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def run_extras(hb, _lib, o, torch, dev, flush, fp8_peak, peaks) -> dict:
+    """Other benchmark configurations, measured in the same run (20 timed launches each)."""
+    res = {}
+
+    def timed(fn, steps=20):
+        ts = time_steps(fn, steps, 3, flush, torch)
+        return statistics.median(ts), min(ts)
+
+    attn = {}
+    for name, (b, h, s, d) in {"B4_H48_S1024_D64": (4, 48, 1024, 64), "B8_H32_S4096_D128": (8, 32, 4096, 128)}.items():
+        g = torch.Generator(device=dev).manual_seed(3)
+        q = torch.randn(b * h, s, d, device=dev, generator=g).to(torch.float8_e4m3fn)
+        k = torch.randn(b * h, s, d, device=dev, generator=g).to(torch.float8_e4m3fn)
+        v = torch.randn(b * h, s, d, device=dev, generator=g).to(torch.float8_e4m3fn).permute(0, 2, 1)
+        outa = torch.empty(b, h, s, d, dtype=torch.float8_e4m3fn, device=dev)
+        med, mn = timed(lambda: hb.fp8_attention(q, k, v, b, h, out=outa))
+        flops = 4.0 * b * h * s * s * d
+        tf = flops / (med * 1e-3) / 1e12
+        attn[name] = {"ms": med, "ms_min": mn, "tflops": tf, "frac_of_measured_fp8_peak": tf / fp8_peak,
+                      "frac_of_nominal_4500": tf / NOMINAL_FP8_TFLOPS,
+                      "hbm_gbs": 4.0 * b * h * s * d / (med * 1e-3) / 1e9}
+        del q, k, v, outa
+    res["attention"] = attn
+
+    mlp = {}
+    kk, nn = 4096, 14336
+    for m in (16, 128, 2048, 16384):
+        g = torch.Generator(device=dev).manual_seed(2)
+        xa = torch.randn(m, kk, device=dev, generator=g).to(torch.float8_e4m3fn)
+        w = torch.randn(nn, kk, device=dev, generator=g) * 0.02
+        w = (w * (448.0 / w.abs().max())).to(torch.float8_e4m3fn).t()
+        outm = torch.empty(m, nn, dtype=torch.bfloat16, device=dev)
+        med, mn = timed(lambda: hb.fp8_gemm(xa, w, out_dtype=torch.bfloat16, out=outm))
+        flops = 2.0 * m * nn * kk
+        byts = m * kk + kk * nn + 2 * m * nn
+        tf = flops / (med * 1e-3) / 1e12
+        gbs = byts / (med * 1e-3) / 1e9
+        mlp[f"M{m}"] = {"ms": med, "ms_min": mn, "tflops": tf, "hbm_gbs": gbs,
+                        "frac_of_measured_fp8_peak": tf / fp8_peak, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
+        del xa, w, outm
+    res["mlp_K4096_N14336"] = mlp
+
+    # cuBLASLt on the same workload, for context (the reference's GPU baseline, examples/fp8_gemm.py:61-78)
+    try:
+        x, y = o.gemm_inputs(M, N, K, seed=1)
+        xd = x.to(dev)
+        yd = y.t().contiguous().to(dev).t()
+        one = torch.tensor(1.0, device=dev)
+        med, mn = timed(lambda: torch._scaled_mm(xd, yd, one, one, use_fast_accum=False, out_dtype=torch.bfloat16))
+        res["cublaslt_scaled_mm_8192"] = {"ms": med, "tflops": GEMM_FLOPS / (med * 1e-3) / 1e12}
+    except Exception as e:  # context only
+        res["cublaslt_scaled_mm_8192"] = {"error": str(e)[:120]}
+    return res
+
+
+if __name__ == "__main__":
+    main()
