@@ -52,62 +52,77 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs (read-only)."""
+    """Samples SM clock, power and throttle reasons through NVML (read-only queries) in a
+    background thread while the timed region runs."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int) -> None:
+    def __init__(self, index: int, period_s: float = 0.002) -> None:
         self.index = index
-        self.proc = None
-        self.lines = []
+        self.period_s = period_s
+        self.samples = []
+        self.reasons = set()
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+        self._handle = None
+        self.sm_max = None
 
     def start(self) -> None:
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
 
-    def _read(self) -> None:
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            pynvml.nvmlInit()
+            # honour CUDA_VISIBLE_DEVICES when it lists indices
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = self.index
+            if visible:
+                ids = [v.strip() for v in visible.split(",") if v.strip()]
+                if self.index < len(ids) and ids[self.index].isdigit():
+                    phys = int(ids[self.index])
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+        except Exception:
+            self._nvml = None
+            return
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _run(self) -> None:
+        nv = self._nvml
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(
+            nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self._stop.is_set():
+            try:
+                sm = float(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                power = nv.nvmlDeviceGetPowerUsage(self._handle) / 1000.0
+                mask = int(get_reasons(self._handle))
+                self.samples.append((power, sm))
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period_s)
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-                power.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        # the median over the busiest half of the samples = the clock under load
-        busy = sorted(zip(power, sm))[len(sm) // 2:] if sm else []
+        if self._nvml is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"], "samples": 0}
+        self._stop.set()
+        self._thread.join(timeout=2)
+        sm = [s for _, s in self.samples]
         return {
-            "sm_mhz": statistics.median(s for _, s in busy) if busy else None,
-            "sm_max_mhz": max(mx) if mx else None,
-            "power_w_max": max(power) if power else None,
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_min_mhz": min(sm) if sm else None,
+            "sm_max_mhz": self.sm_max,
+            "power_w_max": max(p for p, _ in self.samples) if self.samples else None,
             "samples": len(sm),
-            "reasons": sorted(reasons),
+            "reasons": sorted(self.reasons),
         }
 
 
@@ -215,6 +230,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the attention / MLP-shape sections")
+    ap.add_argument("--only", default=None, help="time just one named workload and exit: " + ", ".join(WORKLOADS))
+    ap.add_argument("--config", type=int, default=None, help="tile-config id for --only (default: table choice)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -236,6 +253,9 @@ def main() -> None:
         raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    if args.only is not None:
+        run_only(args, torch, dev, hb, _lib)
+        return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     warmup = max(args.warmup, 3)
@@ -397,6 +417,56 @@ def main() -> None:
 TRAFFIC_BYTES_PER_LAUNCH = None
 
 
+ATTN_SHAPES = {"attn_B4_H48_S1024_D64": (4, 48, 1024, 64), "attn_B8_H32_S4096_D128": (8, 32, 4096, 128)}
+MLP_M = (16, 128, 2048, 16384)
+MLP_K, MLP_N = 4096, 14336
+
+
+def make_workload(name: str, torch, dev, hb, config=None):
+    """Build one named workload on the device: returns (launch fn, flops, algorithmic bytes)."""
+    if name == "gemm_8192":
+        g = torch.Generator(device=dev).manual_seed(1)
+        xa = torch.randn(M, K, device=dev, generator=g).to(torch.float8_e4m3fn)
+        ya = torch.randn(N, K, device=dev, generator=g).to(torch.float8_e4m3fn).t()
+        outg = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        return (lambda: hb.fp8_gemm(xa, ya, out_dtype=torch.bfloat16, out=outg, config=config),
+                GEMM_FLOPS, M * K + K * N + 2 * M * N)
+    if name in ATTN_SHAPES:
+        b, h, s, d = ATTN_SHAPES[name]
+        g = torch.Generator(device=dev).manual_seed(3)
+        q = torch.randn(b * h, s, d, device=dev, generator=g).to(torch.float8_e4m3fn)
+        k = torch.randn(b * h, s, d, device=dev, generator=g).to(torch.float8_e4m3fn)
+        v = torch.randn(b * h, s, d, device=dev, generator=g).to(torch.float8_e4m3fn).permute(0, 2, 1)
+        outa = torch.empty(b, h, s, d, dtype=torch.float8_e4m3fn, device=dev)
+        return (lambda: hb.fp8_attention(q, k, v, b, h, out=outa, config=config),
+                4.0 * b * h * s * s * d, 4 * b * h * s * d)
+    if name.startswith("mlp_M"):
+        m = int(name[5:])
+        g = torch.Generator(device=dev).manual_seed(2)
+        xa = torch.randn(m, MLP_K, device=dev, generator=g).to(torch.float8_e4m3fn)
+        w = torch.randn(MLP_N, MLP_K, device=dev, generator=g) * 0.02
+        w = (w * (448.0 / w.abs().max())).to(torch.float8_e4m3fn).t()
+        outm = torch.empty(m, MLP_N, dtype=torch.bfloat16, device=dev)
+        return (lambda: hb.fp8_gemm(xa, w, out_dtype=torch.bfloat16, out=outm, config=config),
+                2.0 * m * MLP_N * MLP_K, m * MLP_K + MLP_K * MLP_N + 2 * m * MLP_N)
+    raise SystemExit(f"unknown workload {name!r}")
+
+
+WORKLOADS = ["gemm_8192", *ATTN_SHAPES, *(f"mlp_M{m}" for m in MLP_M)]
+
+
+def run_only(args, torch, dev, hb, _lib) -> None:
+    """`--only NAME`: time one named workload (used for sweeps and as the command under ncu)."""
+    fn, flops, byts = make_workload(args.only, torch, dev, hb, args.config)
+    flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    ts = time_steps(fn, args.steps, max(args.warmup, 3), flush_buf.zero_, torch)
+    torch.cuda.synchronize()
+    _lib.check_status(dev.index)
+    med = statistics.median(ts)
+    print(json.dumps({"only": args.only, "config": args.config, "steps": args.steps, "ms": med, "ms_min": min(ts),
+                      "tflops": flops / (med * 1e-3) / 1e12, "gbs": byts / (med * 1e-3) / 1e9}), flush=True)
+
+
 def run_extras(hb, _lib, o, torch, dev, flush, fp8_peak, peaks) -> dict:
     """Other benchmark configurations, measured in the same run (20 timed launches each)."""
     res = {}
@@ -405,39 +475,16 @@ def run_extras(hb, _lib, o, torch, dev, flush, fp8_peak, peaks) -> dict:
         ts = time_steps(fn, steps, 3, flush, torch)
         return statistics.median(ts), min(ts)
 
-    attn = {}
-    for name, (b, h, s, d) in {"B4_H48_S1024_D64": (4, 48, 1024, 64), "B8_H32_S4096_D128": (8, 32, 4096, 128)}.items():
-        g = torch.Generator(device=dev).manual_seed(3)
-        q = torch.randn(b * h, s, d, device=dev, generator=g).to(torch.float8_e4m3fn)
-        k = torch.randn(b * h, s, d, device=dev, generator=g).to(torch.float8_e4m3fn)
-        v = torch.randn(b * h, s, d, device=dev, generator=g).to(torch.float8_e4m3fn).permute(0, 2, 1)
-        outa = torch.empty(b, h, s, d, dtype=torch.float8_e4m3fn, device=dev)
-        med, mn = timed(lambda: hb.fp8_attention(q, k, v, b, h, out=outa))
-        flops = 4.0 * b * h * s * s * d
-        tf = flops / (med * 1e-3) / 1e12
-        attn[name] = {"ms": med, "ms_min": mn, "tflops": tf, "frac_of_measured_fp8_peak": tf / fp8_peak,
-                      "frac_of_nominal_4500": tf / NOMINAL_FP8_TFLOPS,
-                      "hbm_gbs": 4.0 * b * h * s * d / (med * 1e-3) / 1e9}
-        del q, k, v, outa
-    res["attention"] = attn
-
-    mlp = {}
-    kk, nn = 4096, 14336
-    for m in (16, 128, 2048, 16384):
-        g = torch.Generator(device=dev).manual_seed(2)
-        xa = torch.randn(m, kk, device=dev, generator=g).to(torch.float8_e4m3fn)
-        w = torch.randn(nn, kk, device=dev, generator=g) * 0.02
-        w = (w * (448.0 / w.abs().max())).to(torch.float8_e4m3fn).t()
-        outm = torch.empty(m, nn, dtype=torch.bfloat16, device=dev)
-        med, mn = timed(lambda: hb.fp8_gemm(xa, w, out_dtype=torch.bfloat16, out=outm))
-        flops = 2.0 * m * nn * kk
-        byts = m * kk + kk * nn + 2 * m * nn
+    def entry(name):
+        fn, flops, byts = make_workload(name, torch, dev, hb)
+        med, mn = timed(fn)
         tf = flops / (med * 1e-3) / 1e12
         gbs = byts / (med * 1e-3) / 1e9
-        mlp[f"M{m}"] = {"ms": med, "ms_min": mn, "tflops": tf, "hbm_gbs": gbs,
-                        "frac_of_measured_fp8_peak": tf / fp8_peak, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
-        del xa, w, outm
-    res["mlp_K4096_N14336"] = mlp
+        return {"ms": med, "ms_min": mn, "tflops": tf, "hbm_gbs": gbs, "frac_of_measured_fp8_peak": tf / fp8_peak,
+                "frac_of_nominal_4500": tf / NOMINAL_FP8_TFLOPS, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
+
+    res["attention"] = {name: entry(name) for name in ATTN_SHAPES}
+    res["mlp_K4096_N14336"] = {f"M{m}": entry(f"mlp_M{m}") for m in MLP_M}
 
     # cuBLASLt on the same workload, for context (the reference's GPU baseline, examples/fp8_gemm.py:61-78)
     try:
