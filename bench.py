@@ -431,6 +431,13 @@ def make_workload(name: str, torch, dev, hb, config=None):
         outg = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         return (lambda: hb.fp8_gemm(xa, ya, out_dtype=torch.bfloat16, out=outg, config=config),
                 GEMM_FLOPS, M * K + K * N + 2 * M * N)
+    if name == "cublaslt_8192":  # context only: torch._scaled_mm on the same workload
+        g = torch.Generator(device=dev).manual_seed(1)
+        xa = torch.randn(M, K, device=dev, generator=g).to(torch.float8_e4m3fn)
+        ya = torch.randn(N, K, device=dev, generator=g).to(torch.float8_e4m3fn).t()
+        one = torch.tensor(1.0, device=dev)
+        return (lambda: torch._scaled_mm(xa, ya, one, one, use_fast_accum=False, out_dtype=torch.bfloat16),
+                GEMM_FLOPS, M * K + K * N + 2 * M * N)
     if name in ATTN_SHAPES:
         b, h, s, d = ATTN_SHAPES[name]
         g = torch.Generator(device=dev).manual_seed(3)
@@ -452,7 +459,7 @@ def make_workload(name: str, torch, dev, hb, config=None):
     raise SystemExit(f"unknown workload {name!r}")
 
 
-WORKLOADS = ["gemm_8192", *ATTN_SHAPES, *(f"mlp_M{m}" for m in MLP_M)]
+WORKLOADS = ["gemm_8192", *ATTN_SHAPES, *(f"mlp_M{m}" for m in MLP_M), "cublaslt_8192"]
 
 
 def run_only(args, torch, dev, hb, _lib) -> None:

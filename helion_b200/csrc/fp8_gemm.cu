@@ -266,24 +266,273 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------------------
+// CTA-pair variant: two CTAs on one TPC compute one 256 x 256 tile with M = 256 UMMAs
+// (tcgen05.mma.cta_group::2).  Each CTA loads its own 128 rows of x and HALF of the y tile (128
+// columns), so a pair moves 64 KB per 128-deep K block for 256x256 outputs -- half the L2->SM
+// traffic and half the smem read rate per flop of the 128x256 single-CTA tile -- and 6-7 stages fit.
+//
+//   both CTAs, warp 0     TMA producer for the CTA's own smem; completion bytes of BOTH CTAs are
+//                         counted on the leader's `full` barrier
+//   leader CTA, warp 1    issues the MMAs; tcgen05.commit signals `empty` / `acc_full` in each CTA
+//   both CTAs, warps 2-5  epilogue of the CTA's own 128 accumulator rows; one arrival per warp on the
+//                         leader's `acc_empty` barrier (remote arrive from the peer)
+// ------------------------------------------------------------------------------------------------
+template <int STAGES>
+struct PairLayout {
+  static constexpr int A_BYTES = BM * BK;   // 128 rows of x
+  static constexpr int B_BYTES = 128 * BK;  // 128 of the tile's 256 columns of y
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 5;
+  static constexpr int BAR_OFFSET = RING_BYTES;
+  static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;
+  static constexpr int SMEM_BYTES = MISC_OFFSET + 16 + 1024;
+  static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+};
+
+constexpr int PAIR_BM = 256;
+constexpr int PAIR_BN = 256;
+
+template <int STAGES, bool B_MN_MAJOR, int OUT_DT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     void* out, int M, int N, int K, int64_t ldc, int group_m, uint32_t* status) {
+  using L = PairLayout<STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* full = bars;                       // used in the leader only
+  uint64_t* empty = bars + STAGES;             // one set per CTA
+  uint64_t* acc_full = bars + 2 * STAGES;      // one set per CTA
+  uint64_t* acc_empty = bars + 2 * STAGES + 2; // used in the leader only (8 arrivals: 4 warps x 2 CTAs)
+  uint64_t* drain = bars + 2 * STAGES + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFFSET + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int m_tiles = (M + PAIR_BM - 1) / PAIR_BM;
+  const int n_tiles = (N + PAIR_BN - 1) / PAIR_BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + BK - 1) / BK;
+  const WaitCtx wctx{abort_flag, status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 8);
+    }
+    mbar_init(drain, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, L::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) --------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, group_m);
+        const int row0 = tc.m_blk * PAIR_BM + static_cast<int>(rank) * 128;
+        const int col0 = tc.n_blk * PAIR_BN + static_cast<int>(rank) * 128;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u, wctx, SITE_GEMM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + s * L::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + L::A_BYTES;
+          const uint32_t full_leader = map_to_cta(smem_u32(&full[s]), 0);
+          if (leader) mbar_arrive_expect_tx(&full[s], 2 * L::STAGE_BYTES);
+          tma_load_2d_pair(a_dst, &tmap_a, full_leader, kb * BK, row0);
+          if constexpr (!B_MN_MAJOR) {
+            tma_load_2d_pair(b_dst, &tmap_b, full_leader, kb * BK, col0);
+          } else {
+            tma_load_2d_pair(b_dst, &tmap_b, full_leader, col0, kb * BK);
+          }
+        }
+      }
+      if (!ok && leader) {
+        // Abort path: the leader's `full` barriers count the bytes of both CTAs; let them land.
+        const uint32_t back = it < static_cast<uint32_t>(STAGES) ? it : static_cast<uint32_t>(STAGES);
+        for (uint32_t j = it - back; j < it; ++j) mbar_drain(&full[j % STAGES], (j / STAGES) & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader CTA only) -----------------------------
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_e4m3(PAIR_BM, PAIR_BN, false, B_MN_MAJOR);
+      uint32_t it = 0;
+      uint32_t tile_iter = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1u;
+        const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1u, wctx, SITE_GEMM_ACC_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * PAIR_BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&full[s], ph, wctx, SITE_GEMM_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + L::A_BYTES;
+          const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024, SWZ_128B);
+          const uint64_t b_desc = B_MN_MAJOR ? make_smem_desc(b_addr, 1024, 1024, SWZ_128B)
+                                             : make_smem_desc(b_addr, 16, 1024, SWZ_128B);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t ad = desc_advance(a_desc, k * UMMA_K);
+            const uint64_t bd = desc_advance(b_desc, B_MN_MAJOR ? k * UMMA_K * 128 : k * UMMA_K);
+            umma_f8_ss_pair(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          // the stage is free in BOTH CTAs once these MMAs have read it
+          const uint32_t e_local = smem_u32(&empty[s]);
+          umma_commit_pair(e_local);
+          umma_commit_pair(map_to_cta(e_local, 1));
+        }
+        if (ok) {
+          const uint32_t f_local = smem_u32(&acc_full[acc]);
+          umma_commit_pair(f_local);
+          umma_commit_pair(map_to_cta(f_local, 1));
+        }
+      }
+      if (!ok) {
+        umma_commit_pair(smem_u32(drain));
+        mbar_drain(drain, 0);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- epilogue (both CTAs) -------------------------------------
+    const int quarter = warp & 3;
+    uint32_t tile_iter = 0;
+    for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++tile_iter) {
+      const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, group_m);
+      const uint32_t acc = tile_iter & 1u;
+      const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+      bool ok = mbar_wait(&acc_full[acc], acc_ph, wctx, SITE_GEMM_ACC_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = tc.m_blk * PAIR_BM + static_cast<int>(rank) * 128 + quarter * 32 + lane;
+      const int64_t row_off = static_cast<int64_t>(row) * ldc;
+      const uint32_t t_row = tmem_base + acc * PAIR_BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 2
+      for (int c = 0; c < PAIR_BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c, r);
+        tmem_wait_ld();
+        const int col0 = tc.n_blk * PAIR_BN + c;
+        if (row < M && col0 < N) store_row_chunk<OUT_DT>(out, row_off, col0, N, r);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+    }
+  }
+
+  // ------------------------------- teardown ----------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still use it
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, L::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // tile-config table
 // ------------------------------------------------------------------------------------------------
 struct GemmConfig {
-  int bn;
+  int bn;        // tile width (columns of out per tile)
   int stages;
-  int group_m;
+  int group_m;   // row blocks per rasterisation group
+  bool pair;     // CTA-pair kernel (256 x 256 tiles) instead of the single-CTA kernel (128 x bn)
   const char* note;
 };
 
 const GemmConfig kGemmConfigs[] = {
-    {256, 4, 8, "128x256x128 tiles, 4 stages, group_m 8: large tensor-bound problems"},
-    {128, 6, 8, "128x128x128 tiles, 6 stages, group_m 8: mid-size problems, better wave fill"},
-    {64, 8, 8, "128x64x128 tiles, 8 stages, group_m 8: small N / many more tiles (column-major y only)"},
-    {256, 4, 16, "128x256x128 tiles, 4 stages, group_m 16"},
-    {256, 4, 4, "128x256x128 tiles, 4 stages, group_m 4"},
-    {128, 6, 16, "128x128x128 tiles, 6 stages, group_m 16"},
+    {256, 4, 8, false, "1 CTA, 128x256x128 tiles, 4 stages, group_m 8"},
+    {128, 6, 8, false, "1 CTA, 128x128x128 tiles, 6 stages, group_m 8: small problems, better wave fill"},
+    {64, 8, 8, false, "1 CTA, 128x64x128 tiles, 8 stages, group_m 8: very small N (column-major y only)"},
+    {256, 4, 16, false, "1 CTA, 128x256x128 tiles, 4 stages, group_m 16"},
+    {256, 4, 4, false, "1 CTA, 128x256x128 tiles, 4 stages, group_m 4"},
+    {128, 6, 16, false, "1 CTA, 128x128x128 tiles, 6 stages, group_m 16"},
+    {256, 6, 8, true, "CTA pair, 256x256x128 tiles, 6 stages, group_m 8 (of 256-row blocks)"},
+    {256, 7, 8, true, "CTA pair, 256x256x128 tiles, 7 stages, group_m 8"},
+    {256, 7, 4, true, "CTA pair, 256x256x128 tiles, 7 stages, group_m 4"},
+    {256, 7, 16, true, "CTA pair, 256x256x128 tiles, 7 stages, group_m 16"},
+    {256, 6, 4, true, "CTA pair, 256x256x128 tiles, 6 stages, group_m 4"},
 };
 constexpr int kNumGemmConfigs = sizeof(kGemmConfigs) / sizeof(kGemmConfigs[0]);
+
+template <int STAGES, bool B_MN, int OUT_DT>
+int launch_pair_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
+  using L = PairLayout<STAGES>;
+  auto kernel = fp8_gemm_pair_kernel<STAGES, B_MN, OUT_DT>;
+  static bool attr_set[64] = {};
+  if (!attr_set[a.device]) {
+    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
+    attr_set[a.device] = true;
+  }
+  const int64_t m_tiles = (a.M + PAIR_BM - 1) / PAIR_BM;
+  const int64_t n_tiles = (a.N + PAIR_BN - 1) / PAIR_BN;
+  const int64_t num_tiles = m_tiles * n_tiles;
+  const int pairs = static_cast<int>(std::min<int64_t>(num_tiles, ctx->num_sms / 2));
+  kernel<<<2 * pairs, NUM_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, a.out, static_cast<int>(a.M),
+                                                              static_cast<int>(a.N), static_cast<int>(a.K), a.ldc,
+                                                              group_m, ctx->status_dev);
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB200_OK;
+}
+
+template <int STAGES, bool B_MN>
+int launch_pair_by_dtype(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
+  switch (a.out_dtype) {
+    case HB200_DT_FP16:
+      return launch_pair_instance<STAGES, B_MN, HB200_DT_FP16>(a, ctx, ta, tb, group_m);
+    case HB200_DT_BF16:
+      return launch_pair_instance<STAGES, B_MN, HB200_DT_BF16>(a, ctx, ta, tb, group_m);
+    case HB200_DT_FP32:
+      return launch_pair_instance<STAGES, B_MN, HB200_DT_FP32>(a, ctx, ta, tb, group_m);
+    default:
+      return set_error(HB200_ERR_BAD_DTYPE, "fp8_gemm: unsupported out_dtype");
+  }
+}
 
 template <int BN, int STAGES, bool B_MN, int OUT_DT>
 int launch_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
@@ -325,30 +574,37 @@ int gemm_num_configs() { return kNumGemmConfigs; }
 int gemm_describe_config(int cfg_id, char* buf, int buf_len) {
   if (cfg_id < 0 || cfg_id >= kNumGemmConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: no such config");
   const GemmConfig& c = kGemmConfigs[cfg_id];
-  return std::snprintf(buf, buf_len, "gemm cfg %d: BM=128 BN=%d BK=128 stages=%d group_m=%d (%s)", cfg_id, c.bn,
-                       c.stages, c.group_m, c.note);
+  return std::snprintf(buf, buf_len, "gemm cfg %d: BM=%d BN=%d BK=128 stages=%d group_m=%d (%s)", cfg_id,
+                       c.pair ? 256 : 128, c.bn, c.stages, c.group_m, c.note);
 }
 
 size_t gemm_workspace_bytes(int64_t, int64_t, int64_t, int, int) { return 0; }
 
-// Chooses the tile width that minimises (waves x tile width), i.e. the time of the persistent
-// schedule in units of 128-row MMA columns; ties go to the wider tile (less smem traffic per flop).
+// Chooses the table row with the smallest estimated time of the persistent schedule:
+//   waves x (outputs one SM produces per tile) / (measured tensor-pipe efficiency of the tile shape).
+// Efficiencies are the tensor-pipe-active fractions measured at 8192^3 on B200 (128x256: 0.75,
+// 128x128: 0.51, 128x64: 0.26, CTA pair 256x256: 0.78); a pair tile occupies two SMs.
 int gemm_select_config(int64_t M, int64_t N, int64_t K, bool y_colmajor, int out_dtype, int num_sms) {
   (void)K;
   (void)out_dtype;
-  const int64_t m_tiles = (M + BM - 1) / BM;
-  int best = 0;
-  int64_t best_cost = -1;
-  const int candidates[3] = {0, 1, 2};
-  for (int idx : candidates) {
-    const GemmConfig& c = kGemmConfigs[idx];
-    if (!y_colmajor && c.bn < 128) continue;
-    const int64_t tiles = m_tiles * ((N + c.bn - 1) / c.bn);
-    const int64_t waves = (tiles + num_sms - 1) / num_sms;
-    const int64_t cost = waves * c.bn;
+  struct Candidate {
+    int cfg;
+    double eff;
+  };
+  const Candidate candidates[4] = {{3, 0.75}, {1, 0.51}, {2, 0.26}, {7, 0.78}};
+  int best = 3;
+  double best_cost = -1.0;
+  for (const Candidate& cand : candidates) {
+    const GemmConfig& c = kGemmConfigs[cand.cfg];
+    if (!y_colmajor && !c.pair && c.bn < 128) continue;
+    const int64_t bm = c.pair ? PAIR_BM : BM;
+    const int64_t slots = c.pair ? num_sms / 2 : num_sms;
+    const int64_t tiles = ((M + bm - 1) / bm) * ((N + c.bn - 1) / c.bn);
+    const int64_t waves = (tiles + slots - 1) / slots;
+    const double cost = static_cast<double>(waves) * 128.0 * c.bn / cand.eff;
     if (best_cost < 0 || cost < best_cost) {
       best_cost = cost;
-      best = idx;
+      best = cand.cfg;
     }
   }
   return best;
@@ -374,7 +630,7 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
   if (a.y_colmajor) {
     const uint64_t dims[2] = {static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.N)};
     const uint64_t strides[1] = {static_cast<uint64_t>(a.ldb)};
-    const uint32_t box[2] = {BK, static_cast<uint32_t>(c.bn)};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(c.pair ? 128 : c.bn)};
     int rc = encode_tmap_u8(&tb, a.y, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != HB200_OK) return rc;
   } else {
@@ -385,6 +641,14 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
     if (rc != HB200_OK) return rc;
   }
 
+  if (c.pair) {
+    if (c.stages == 6) {
+      return a.y_colmajor ? launch_pair_by_dtype<6, false>(a, ctx, ta, tb, c.group_m)
+                          : launch_pair_by_dtype<6, true>(a, ctx, ta, tb, c.group_m);
+    }
+    return a.y_colmajor ? launch_pair_by_dtype<7, false>(a, ctx, ta, tb, c.group_m)
+                        : launch_pair_by_dtype<7, true>(a, ctx, ta, tb, c.group_m);
+  }
   if (a.y_colmajor) {
     switch (c.bn) {
       case 256:
