@@ -40,6 +40,10 @@ enum WaitSite : uint32_t {
   SITE_ATTN_PV_DONE = 17,
   SITE_ATTN_O_FULL = 18,
   SITE_ATTN_TILE_DONE = 19,
+  SITE_ATTN_XCHG = 20,
+  SITE_ATTN_XU_LOCK = 23,
+  SITE_ATTN_ALPHA = 21,
+  SITE_ATTN_O_READY = 22,
   SITE_SPLITK = 30,
 };
 
@@ -160,6 +164,27 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   for (;;) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
     if (((++spins) & 0xffu) == 0u) {
+      if (*ctx.abort_flag) return false;
+      if (global_timer_ns() - t0 > HB_WAIT_LIMIT_NS) {
+        record_timeout(ctx, site);
+        return false;
+      }
+    }
+  }
+}
+
+// Same contract as mbar_wait for waits that are not latency-critical (a producer waiting for a free
+// slot, an MMA issuer waiting for operands that are needed much later): sleeps between polls so that
+// the polling thread does not take issue slots from the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, uint32_t site,
+                                                  uint32_t sleep_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity)) return true;
+    if (((++spins) & 0x3fu) == 0u) {
       if (*ctx.abort_flag) return false;
       if (global_timer_ns() - t0 > HB_WAIT_LIMIT_NS) {
         record_timeout(ctx, site);
@@ -457,10 +482,70 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
   return static_cast<uint32_t>(pack_e4m3x2(a, b)) | (static_cast<uint32_t>(pack_e4m3x2(c, d)) << 16);
 }
 
+// ---- packed fp32 pairs (one 64-bit register = two floats; sm_100 issues these as one instruction)
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack2f(float lo, float hi) { return pack2(__float_as_uint(lo), __float_as_uint(hi)); }
+__device__ __forceinline__ void unpack2(uint64_t v, uint32_t& lo, uint32_t& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// 2^x for a pair of x <= 0 through the MUFU unit.
+__device__ __forceinline__ uint64_t exp2_pair_mufu(uint64_t x2) {
+  uint32_t lo, hi;
+  unpack2(x2, lo, hi);
+  return pack2f(fast_exp2(__uint_as_float(lo)), fast_exp2(__uint_as_float(hi)));
+}
+
+// 2^x for a pair of x <= 0 on the FMA / ALU pipes only (no MUFU): round-to-nearest split
+// x = n + f with |f| <= 0.5 by the 1.5*2^23 trick, degree-3 minimax polynomial for 2^f
+// (relative error 7.5e-5), then n is added into the exponent field.  x is clamped at -126 so that
+// the exponent arithmetic cannot wrap (2^-126 rounds to zero in every use here).
+__device__ __forceinline__ uint64_t exp2_pair_poly(uint64_t x2) {
+  uint32_t xl, xh;
+  unpack2(x2, xl, xh);
+  const float xcl = fmaxf(__uint_as_float(xl), -126.0f);
+  const float xch = fmaxf(__uint_as_float(xh), -126.0f);
+  const uint64_t x = pack2f(xcl, xch);
+  const uint64_t magic = pack2f(12582912.0f, 12582912.0f);
+  const uint64_t neg_magic = pack2f(-12582912.0f, -12582912.0f);
+  const uint64_t neg_one = pack2f(-1.0f, -1.0f);
+  const uint64_t xr = fadd2(x, magic);        // low mantissa bits now hold round(x)
+  const uint64_t nf = fadd2(xr, neg_magic);   // round(x) as a float
+  const uint64_t f = ffma2(nf, neg_one, x);   // x - round(x), in [-0.5, 0.5]
+  uint64_t p = ffma2(pack2f(0.055171605f, 0.055171605f), f, pack2f(0.24261111f, 0.24261111f));
+  p = ffma2(p, f, pack2f(0.69326097f, 0.69326097f));
+  p = ffma2(p, f, pack2f(0.99992806f, 0.99992806f));
+  uint32_t pl, ph, rl, rh;
+  unpack2(p, pl, ph);
+  unpack2(xr, rl, rh);
+  pl += rl << 23;  // exponent += round(x); the bits above the exponent wrap away
+  ph += rh << 23;
+  return pack2(pl, ph);
 }
 
 }  // namespace hb

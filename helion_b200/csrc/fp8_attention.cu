@@ -55,7 +55,7 @@ struct AttnLayout {
 __device__ __forceinline__ void reg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
 __device__ __forceinline__ void reg_inc_200() { asm volatile("setmaxnreg.inc.sync.aligned.u32 200;"); }
 
-template <int D, bool V_KMAJOR, int OUT_DT>
+template <int D, bool V_KMAJOR, int OUT_DT, int POLY_OF8, bool LAZY>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, void* out, int BH, int S, int64_t out_stride_bh,
@@ -126,7 +126,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
           const int bh = tile / m_tiles;
           const int mt = tile - bh * m_tiles;
-          if (!mbar_wait(q_empty, (tile_iter & 1u) ^ 1u, wctx, SITE_ATTN_Q)) {
+          if (!mbar_wait_relaxed(q_empty, (tile_iter & 1u) ^ 1u, wctx, SITE_ATTN_Q, 200)) {
             ok = false;
             break;
           }
@@ -137,7 +137,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             for (int kv = 0; kv < 2; ++kv, ++slot_it) {
               const uint32_t s = slot_it % ST;
               const uint32_t ph = (slot_it / ST) & 1u;
-              if (!mbar_wait(&kv_empty[s], ph ^ 1u, wctx, SITE_ATTN_KV_EMPTY)) {
+              if (!mbar_wait_relaxed(&kv_empty[s], ph ^ 1u, wctx, SITE_ATTN_KV_EMPTY, 200)) {
                 ok = false;
                 break;
               }
@@ -180,8 +180,8 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         // Q K^T of one step: waits for the K tile (and for S to be free), issues D/32 MMAs.
         auto issue_qk = [&](uint32_t k_slot_it, uint32_t step_g, bool last_of_tile) -> bool {
           const uint32_t s = k_slot_it % ST;
-          if (!mbar_wait(&kv_full[s], (k_slot_it / ST) & 1u, wctx, SITE_ATTN_K_FULL)) return false;
-          if (step_g > 0 && !mbar_wait(s_free, (step_g - 1u) & 1u, wctx, SITE_ATTN_S_FREE)) return false;
+          if (!mbar_wait_relaxed(&kv_full[s], (k_slot_it / ST) & 1u, wctx, SITE_ATTN_K_FULL, 100)) return false;
+          if (step_g > 0 && !mbar_wait_relaxed(s_free, (step_g - 1u) & 1u, wctx, SITE_ATTN_S_FREE, 100)) return false;
           tc_fence_after_sync();
           const uint64_t k_desc = make_smem_desc(kv_addr + s * L::TILE_BYTES, 16, SBO_QK, SWZ_QK);
 #pragma unroll
@@ -195,7 +195,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         };
 
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
-          if (!mbar_wait(q_full, tile_iter & 1u, wctx, SITE_ATTN_Q)) {
+          if (!mbar_wait_relaxed(q_full, tile_iter & 1u, wctx, SITE_ATTN_Q, 100)) {
             ok = false;
             break;
           }
@@ -212,8 +212,8 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             }
             // O (+)= P V
             const uint32_t vs = (slot_it + 1) % ST;
-            if (!mbar_wait(&kv_full[vs], ((slot_it + 1) / ST) & 1u, wctx, SITE_ATTN_V_FULL) ||
-                !mbar_wait(p_full, g & 1u, wctx, SITE_ATTN_P_FULL)) {
+            if (!mbar_wait_relaxed(&kv_full[vs], ((slot_it + 1) / ST) & 1u, wctx, SITE_ATTN_V_FULL, 100) ||
+                !mbar_wait_relaxed(p_full, g & 1u, wctx, SITE_ATTN_P_FULL, 100)) {
               ok = false;
               break;
             }
@@ -281,41 +281,57 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             }
           }
         }
+        // row max: 3-input max, four independent chains
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, __uint_as_float(s[c][i]));
-            mx1 = fmaxf(mx1, __uint_as_float(s[c][i + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(s[c][i + 2]));
-            mx3 = fmaxf(mx3, __uint_as_float(s[c][i + 3]));
+          for (int i = 0; i < 32; i += 8) {
+            mx0 = fmax3(mx0, __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+            mx1 = fmax3(mx1, __uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3]));
+            mx2 = fmax3(mx2, __uint_as_float(s[c][i + 4]), __uint_as_float(s[c][i + 5]));
+            mx3 = fmax3(mx3, __uint_as_float(s[c][i + 6]), __uint_as_float(s[c][i + 7]));
           }
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        const float m_new = fmaxf(m_i, mx * scale_log2);
+        // Exact mode follows the running max (examples/fp8_attention.py:76-78).  Lazy mode keeps the
+        // previous reference point m_i while the max has grown by at most 2^8: p is then at most
+        // 256 (e4m3 holds 448), O and l stay consistent because both use the same m_i, and the
+        // tensor-memory round trip that rescales O leaves the critical path of almost every step.
+        const float cand = fmaxf(m_i, mx * scale_log2);
+        const bool moved = LAZY ? (cand - m_i > 8.0f) : (cand > m_i);
+        const float m_new = (LAZY && !moved) ? m_i : cand;
         const float alpha = fast_exp2(m_i - m_new);
-        const float neg_m = -m_new;
 
-        // exp2, row sum (from the fp32 values), e4m3 pack
-        float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
+        // p = exp2(s*c - m) on packed pairs; POLY_OF8 of every 8 pairs take the FMA-pipe polynomial
+        // instead of the MUFU unit.  Row sum from the fp32 values; e4m3 pack (4 per word).
+        const uint64_t c2 = pack2f(scale_log2, scale_log2);
+        const uint64_t negm2 = pack2f(-m_new, -m_new);
+        uint64_t sum_a = 0ull, sum_b = 0ull;  // two (0.0f, 0.0f) pairs
         uint32_t packed[32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][i]), scale_log2, neg_m));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][i + 1]), scale_log2, neg_m));
-            const float p2 = fast_exp2(fmaf(__uint_as_float(s[c][i + 2]), scale_log2, neg_m));
-            const float p3 = fast_exp2(fmaf(__uint_as_float(s[c][i + 3]), scale_log2, neg_m));
-            sum0 += p0;
-            sum1 += p1;
-            sum2 += p2;
-            sum3 += p3;
-            packed[c * 8 + i / 4] = pack_e4m3x4(p0, p1, p2, p3);
+            const int pair0 = (c * 32 + i) / 2;
+            const uint64_t t0 = ffma2(pack2(s[c][i], s[c][i + 1]), c2, negm2);
+            const uint64_t t1 = ffma2(pack2(s[c][i + 2], s[c][i + 3]), c2, negm2);
+            const uint64_t p0 = (pair0 % 8) < POLY_OF8 ? exp2_pair_poly(t0) : exp2_pair_mufu(t0);
+            const uint64_t p1 = ((pair0 + 1) % 8) < POLY_OF8 ? exp2_pair_poly(t1) : exp2_pair_mufu(t1);
+            sum_a = fadd2(sum_a, p0);
+            sum_b = fadd2(sum_b, p1);
+            uint32_t a0, a1, b0, b1;
+            unpack2(p0, a0, a1);
+            unpack2(p1, b0, b1);
+            packed[c * 8 + i / 4] =
+                pack_e4m3x4(__uint_as_float(a0), __uint_as_float(a1), __uint_as_float(b0), __uint_as_float(b1));
           }
         }
-        l_i = l_i * alpha + ((sum0 + sum1) + (sum2 + sum3));
+        {
+          uint32_t sl, sh;
+          unpack2(fadd2(sum_a, sum_b), sl, sh);
+          l_i = l_i * alpha + (__uint_as_float(sl) + __uint_as_float(sh));
+        }
 
         // The previous P V must be complete before P (smem) is overwritten or O is rescaled.
         if (g > 0) {
@@ -325,7 +341,6 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           tc_fence_after_sync();
         }
         if (j > 0) {
-          const bool moved = m_new > m_i;
           if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
@@ -416,18 +431,24 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 }
 
 struct AttnConfig {
+  int poly_of8;  // of every 8 pairs of exponentials, how many use the FMA-pipe polynomial
+  bool lazy;     // rescale O only when a row max grew by more than 2^8
   const char* note;
 };
 const AttnConfig kAttnConfigs[] = {
-    {"128 query rows x 128 keys per step, P through shared memory, 2 persistent CTAs per SM"},
+    {0, false, "exact running max (rescale whenever a row max moves), all exp2 on the MUFU unit"},
+    {0, true, "lazy rescale (only when a row max grew by more than 2^8), all exp2 on the MUFU unit"},
+    {2, true, "lazy rescale, 2 of 8 exp2 pairs on the FMA pipes (degree-3 polynomial)"},
+    {4, true, "lazy rescale, 4 of 8 exp2 pairs on the FMA pipes"},
 };
-constexpr int kNumAttnConfigs = 1;
+constexpr int kNumAttnConfigs = 4;
+constexpr int kDefaultAttnConfig = 0;
 
-template <int D, bool V_KMAJOR, int OUT_DT>
-int launch_attn_instance(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, const CUtensorMap& tk,
-                         const CUtensorMap& tv) {
+template <int D, bool V_KMAJOR, int OUT_DT, int POLY_OF8, bool LAZY>
+int launch_attn_poly(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, const CUtensorMap& tk,
+                     const CUtensorMap& tv) {
   using L = AttnLayout<D>;
-  auto kernel = fp8_attention_kernel<D, V_KMAJOR, OUT_DT>;
+  auto kernel = fp8_attention_kernel<D, V_KMAJOR, OUT_DT, POLY_OF8, LAZY>;
   static bool attr_set[64] = {};
   if (!attr_set[a.device]) {
     HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
@@ -442,6 +463,24 @@ int launch_attn_instance(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& t
                                                          a.scale_log2, ctx->status_dev);
   HB_CUDA_CHECK(cudaGetLastError());
   return HB200_OK;
+}
+
+template <int D, bool V_KMAJOR, int OUT_DT>
+int launch_attn_instance(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, const CUtensorMap& tk,
+                         const CUtensorMap& tv) {
+  const int cfg = a.cfg_id < 0 ? kDefaultAttnConfig : a.cfg_id;
+  const AttnConfig& c = kAttnConfigs[cfg];
+  if (!c.lazy) return launch_attn_poly<D, V_KMAJOR, OUT_DT, 0, false>(a, ctx, tq, tk, tv);
+  switch (c.poly_of8) {
+    case 0:
+      return launch_attn_poly<D, V_KMAJOR, OUT_DT, 0, true>(a, ctx, tq, tk, tv);
+    case 2:
+      return launch_attn_poly<D, V_KMAJOR, OUT_DT, 2, true>(a, ctx, tq, tk, tv);
+    case 4:
+      return launch_attn_poly<D, V_KMAJOR, OUT_DT, 4, true>(a, ctx, tq, tk, tv);
+    default:
+      return set_error(HB200_ERR_BAD_CONFIG, "fp8_attention: config has no kernel instance");
+  }
 }
 
 template <int D, bool V_KMAJOR>

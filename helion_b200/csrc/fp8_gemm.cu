@@ -97,7 +97,9 @@ __device__ __forceinline__ void store_row_chunk(void* out, int64_t row_offset_el
 template <int BN, int STAGES, bool B_MN_MAJOR, int OUT_DT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, void* out,
-                int M, int N, int K, int64_t ldc, int group_m, uint32_t* status) {
+                int M, int N, int K, int64_t ldc, int group_m, uint32_t* status, int splits, float* partials) {
+  // splits > 1: split-K.  Work unit u = (tile u % num_tiles, K range u / num_tiles); every unit writes
+  // its fp32 partial tile to partials[split][M][N] and splitk_reduce_kernel sums and converts.
   using L = GemmLayout<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -116,6 +118,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const int n_tiles = (N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
   const int k_blocks = (K + BK - 1) / BK;
+  const int kb_per_split = (k_blocks + splits - 1) / splits;
+  const int num_units = num_tiles * splits;
   const WaitCtx wctx{abort_flag, status};
 
   if (threadIdx.x == 0) {
@@ -148,9 +152,12 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       tma_prefetch_desc(&tmap_b);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, group_m);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        const int split = unit / num_tiles;
+        const TileCoord tc = tile_coord(unit - split * num_tiles, m_tiles, n_tiles, group_m);
+        const int kb_begin = split * kb_per_split;
+        const int kb_end = min(k_blocks, kb_begin + kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(&empty[s], ph ^ 1u, wctx, SITE_GEMM_EMPTY)) {
@@ -187,7 +194,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       uint32_t it = 0;
       uint32_t tile_iter = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++tile_iter) {
+        const int kb_begin = (unit / num_tiles) * kb_per_split;
+        const int kb_end = min(k_blocks, kb_begin + kb_per_split);
         const uint32_t acc = tile_iter & 1u;
         const uint32_t acc_ph = (tile_iter >> 1) & 1u;
         if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1u, wctx, SITE_GEMM_ACC_EMPTY)) {
@@ -196,7 +205,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(&full[s], ph, wctx, SITE_GEMM_FULL)) {
@@ -216,7 +225,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t ad = desc_advance(a_desc, k * UMMA_K);
             const uint64_t bd = desc_advance(b_desc, B_MN_MAJOR ? k * UMMA_K * 128 : k * UMMA_K);
-            umma_f8_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f8_ss(d_tmem, ad, bd, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty[s]);  // smem stage is free once these MMAs have read it
         }
@@ -232,8 +241,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     // ------------------------------- epilogue ------------------------------------------------
     const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
     uint32_t tile_iter = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
-      const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, group_m);
+    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++tile_iter) {
+      const int split = unit / num_tiles;
+      const TileCoord tc = tile_coord(unit - split * num_tiles, m_tiles, n_tiles, group_m);
       const uint32_t acc = tile_iter & 1u;
       const uint32_t acc_ph = (tile_iter >> 1) & 1u;
       bool ok = mbar_wait(&acc_full[acc], acc_ph, wctx, SITE_GEMM_ACC_FULL);
@@ -242,6 +252,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       tc_fence_after_sync();
       const int row = tc.m_blk * BM + quarter * 32 + lane;
       const int64_t row_off = static_cast<int64_t>(row) * ldc;
+      float* part = partials + (static_cast<int64_t>(split) * M + row) * N;  // used when splits > 1
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 2
       for (int c = 0; c < BN; c += 32) {
@@ -249,7 +260,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         tmem_ld_32x32b_x32(t_row + c, r);
         tmem_wait_ld();
         const int col0 = tc.n_blk * BN + c;
-        if (row < M && col0 < N) store_row_chunk<OUT_DT>(out, row_off, col0, N, r);
+        if (row < M && col0 < N) {
+          if (splits > 1) {
+            store_row_chunk<HB200_DT_FP32>(part, 0, col0, N, r);
+          } else {
+            store_row_chunk<OUT_DT>(out, row_off, col0, N, r);
+          }
+        }
       }
       tc_fence_before_sync();
       mbar_arrive(&acc_empty[acc]);
@@ -262,6 +279,37 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc(tmem_base, L::TMEM_COLS);
+  }
+}
+
+// Split-K second pass: out[m, n] = cast(sum over splits of partials[s][m][n]), summed in split order
+// (deterministic).  One thread per 8 consecutive columns.
+template <int OUT_DT>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partials, void* out, int M, int N, int64_t ldc,
+                                     int splits) {
+  const int64_t groups_per_row = N / 8;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(M) * groups_per_row) return;
+  const int64_t row = idx / groups_per_row;
+  const int col = static_cast<int>(idx - row * groups_per_row) * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < splits; ++s) {
+    const float4* src = reinterpret_cast<const float4*>(partials + (static_cast<int64_t>(s) * M + row) * N + col);
+    const float4 a = src[0], b = src[1];
+    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+    acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+  }
+  if constexpr (OUT_DT == HB200_DT_FP32) {
+    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + row * ldc + col);
+    dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  } else {
+    uint32_t p[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      p[j] = (OUT_DT == HB200_DT_BF16) ? pack_bf16x2(acc[2 * j], acc[2 * j + 1]) : pack_f16x2(acc[2 * j], acc[2 * j + 1]);
+    }
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + row * ldc + col) = make_uint4(p[0], p[1], p[2], p[3]);
   }
 }
 
@@ -482,21 +530,25 @@ struct GemmConfig {
   int stages;
   int group_m;   // row blocks per rasterisation group
   bool pair;     // CTA-pair kernel (256 x 256 tiles) instead of the single-CTA kernel (128 x bn)
+  int splits;    // split-K factor (needs a workspace of splits x M x N floats when > 1)
   const char* note;
 };
 
 const GemmConfig kGemmConfigs[] = {
-    {256, 4, 8, false, "1 CTA, 128x256x128 tiles, 4 stages, group_m 8"},
-    {128, 6, 8, false, "1 CTA, 128x128x128 tiles, 6 stages, group_m 8: small problems, better wave fill"},
-    {64, 8, 8, false, "1 CTA, 128x64x128 tiles, 8 stages, group_m 8: very small N (column-major y only)"},
-    {256, 4, 16, false, "1 CTA, 128x256x128 tiles, 4 stages, group_m 16"},
-    {256, 4, 4, false, "1 CTA, 128x256x128 tiles, 4 stages, group_m 4"},
-    {128, 6, 16, false, "1 CTA, 128x128x128 tiles, 6 stages, group_m 16"},
-    {256, 6, 8, true, "CTA pair, 256x256x128 tiles, 6 stages, group_m 8 (of 256-row blocks)"},
-    {256, 7, 8, true, "CTA pair, 256x256x128 tiles, 7 stages, group_m 8"},
-    {256, 7, 4, true, "CTA pair, 256x256x128 tiles, 7 stages, group_m 4"},
-    {256, 7, 16, true, "CTA pair, 256x256x128 tiles, 7 stages, group_m 16"},
-    {256, 6, 4, true, "CTA pair, 256x256x128 tiles, 6 stages, group_m 4"},
+    {256, 4, 8, false, 1, "1 CTA, 128x256x128 tiles, 4 stages, group_m 8"},
+    {128, 6, 8, false, 1, "1 CTA, 128x128x128 tiles, 6 stages, group_m 8: small problems, better wave fill"},
+    {64, 8, 8, false, 1, "1 CTA, 128x64x128 tiles, 8 stages, group_m 8: very small N (column-major y only)"},
+    {256, 4, 16, false, 1, "1 CTA, 128x256x128 tiles, 4 stages, group_m 16"},
+    {256, 4, 4, false, 1, "1 CTA, 128x256x128 tiles, 4 stages, group_m 4"},
+    {128, 6, 16, false, 1, "1 CTA, 128x128x128 tiles, 6 stages, group_m 16"},
+    {256, 6, 8, true, 1, "CTA pair, 256x256x128 tiles, 6 stages, group_m 8 (of 256-row blocks)"},
+    {256, 7, 8, true, 1, "CTA pair, 256x256x128 tiles, 7 stages, group_m 8"},
+    {256, 7, 4, true, 1, "CTA pair, 256x256x128 tiles, 7 stages, group_m 4"},
+    {256, 7, 16, true, 1, "CTA pair, 256x256x128 tiles, 7 stages, group_m 16"},
+    {256, 6, 4, true, 1, "CTA pair, 256x256x128 tiles, 6 stages, group_m 4"},
+    {128, 6, 8, false, 2, "1 CTA, 128x128x128 tiles, split-K 2: skinny M, HBM-bound"},
+    {128, 6, 8, false, 4, "1 CTA, 128x128x128 tiles, split-K 4: skinny M, HBM-bound"},
+    {128, 6, 8, false, 8, "1 CTA, 128x128x128 tiles, split-K 8: skinny M, HBM-bound"},
 };
 constexpr int kNumGemmConfigs = sizeof(kGemmConfigs) / sizeof(kGemmConfigs[0]);
 
@@ -534,8 +586,17 @@ int launch_pair_by_dtype(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& t
   }
 }
 
+// K blocks each split handles and the number of non-empty splits for a requested split factor.
+static int effective_splits(int64_t K, int requested) {
+  const int k_blocks = static_cast<int>((K + BK - 1) / BK);
+  const int want = std::max(1, std::min(requested, k_blocks));
+  const int per = (k_blocks + want - 1) / want;
+  return (k_blocks + per - 1) / per;
+}
+
 template <int BN, int STAGES, bool B_MN, int OUT_DT>
-int launch_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
+int launch_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m,
+                    int splits_requested = 1) {
   using L = GemmLayout<BN, STAGES>;
   auto kernel = fp8_gemm_kernel<BN, STAGES, B_MN, OUT_DT>;
   static bool attr_set[64] = {};
@@ -546,22 +607,39 @@ int launch_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, co
   const int m_tiles = static_cast<int>((a.M + BM - 1) / BM);
   const int n_tiles = static_cast<int>((a.N + BN - 1) / BN);
   const int64_t num_tiles = static_cast<int64_t>(m_tiles) * n_tiles;
-  const int grid = static_cast<int>(std::min<int64_t>(num_tiles, ctx->num_sms));
+  const int splits = effective_splits(a.K, splits_requested);
+  if (splits > 1) {
+    const size_t need = static_cast<size_t>(splits) * a.M * a.N * sizeof(float);
+    if (a.workspace == nullptr || a.workspace_bytes < need || (reinterpret_cast<uintptr_t>(a.workspace) & 15u)) {
+      return set_error(HB200_ERR_WORKSPACE, "fp8_gemm: this split-K config needs a 16-byte aligned workspace of " +
+                                                std::to_string(need) + " bytes (hb200_fp8_gemm_workspace_bytes)");
+    }
+  }
+  const int grid = static_cast<int>(std::min<int64_t>(num_tiles * splits, ctx->num_sms));
   kernel<<<grid, NUM_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, a.out, static_cast<int>(a.M), static_cast<int>(a.N),
-                                                         static_cast<int>(a.K), a.ldc, group_m, ctx->status_dev);
+                                                         static_cast<int>(a.K), a.ldc, group_m, ctx->status_dev, splits,
+                                                         static_cast<float*>(a.workspace));
   HB_CUDA_CHECK(cudaGetLastError());
+  if (splits > 1) {
+    const int64_t threads_total = a.M * (a.N / 8);
+    const int blocks = static_cast<int>((threads_total + 255) / 256);
+    splitk_reduce_kernel<OUT_DT><<<blocks, 256, 0, a.stream>>>(static_cast<const float*>(a.workspace), a.out,
+                                                              static_cast<int>(a.M), static_cast<int>(a.N), a.ldc, splits);
+    HB_CUDA_CHECK(cudaGetLastError());
+  }
   return HB200_OK;
 }
 
 template <int BN, int STAGES, bool B_MN>
-int launch_by_dtype(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
+int launch_by_dtype(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m,
+                    int splits = 1) {
   switch (a.out_dtype) {
     case HB200_DT_FP16:
-      return launch_instance<BN, STAGES, B_MN, HB200_DT_FP16>(a, ctx, ta, tb, group_m);
+      return launch_instance<BN, STAGES, B_MN, HB200_DT_FP16>(a, ctx, ta, tb, group_m, splits);
     case HB200_DT_BF16:
-      return launch_instance<BN, STAGES, B_MN, HB200_DT_BF16>(a, ctx, ta, tb, group_m);
+      return launch_instance<BN, STAGES, B_MN, HB200_DT_BF16>(a, ctx, ta, tb, group_m, splits);
     case HB200_DT_FP32:
-      return launch_instance<BN, STAGES, B_MN, HB200_DT_FP32>(a, ctx, ta, tb, group_m);
+      return launch_instance<BN, STAGES, B_MN, HB200_DT_FP32>(a, ctx, ta, tb, group_m, splits);
     default:
       return set_error(HB200_ERR_BAD_DTYPE, "fp8_gemm: unsupported out_dtype");
   }
@@ -574,19 +652,23 @@ int gemm_num_configs() { return kNumGemmConfigs; }
 int gemm_describe_config(int cfg_id, char* buf, int buf_len) {
   if (cfg_id < 0 || cfg_id >= kNumGemmConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: no such config");
   const GemmConfig& c = kGemmConfigs[cfg_id];
-  return std::snprintf(buf, buf_len, "gemm cfg %d: BM=%d BN=%d BK=128 stages=%d group_m=%d (%s)", cfg_id,
-                       c.pair ? 256 : 128, c.bn, c.stages, c.group_m, c.note);
+  return std::snprintf(buf, buf_len, "gemm cfg %d: BM=%d BN=%d BK=128 stages=%d group_m=%d split_k=%d (%s)", cfg_id,
+                       c.pair ? 256 : 128, c.bn, c.stages, c.group_m, c.splits, c.note);
 }
 
-size_t gemm_workspace_bytes(int64_t, int64_t, int64_t, int, int) { return 0; }
+size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int cfg_id) {
+  if (cfg_id < 0) cfg_id = gemm_select_config(M, N, K, true, out_dtype, 148);
+  if (cfg_id >= kNumGemmConfigs) return 0;
+  const int splits = effective_splits(K, kGemmConfigs[cfg_id].splits);
+  return splits > 1 ? static_cast<size_t>(splits) * M * N * sizeof(float) : 0;
+}
 
 // Chooses the table row with the smallest estimated time of the persistent schedule:
 //   waves x (outputs one SM produces per tile) / (measured tensor-pipe efficiency of the tile shape).
 // Efficiencies are the tensor-pipe-active fractions measured at 8192^3 on B200 (128x256: 0.75,
 // 128x128: 0.51, 128x64: 0.26, CTA pair 256x256: 0.78); a pair tile occupies two SMs.
-int gemm_select_config(int64_t M, int64_t N, int64_t K, bool y_colmajor, int out_dtype, int num_sms) {
+static int gemm_select_config_nosplit(int64_t M, int64_t N, int64_t K, bool y_colmajor, int num_sms) {
   (void)K;
-  (void)out_dtype;
   struct Candidate {
     int cfg;
     double eff;
@@ -610,9 +692,41 @@ int gemm_select_config(int64_t M, int64_t N, int64_t K, bool y_colmajor, int out
   return best;
 }
 
+// Split-K row of the table for a problem, or -1.  Depends on the sizes only (not on layouts), so the
+// workspace query and the launch agree.  Skinny problems (one row block, less than a wave of 128-wide
+// tiles) are HBM-bound on reading y: splitting K puts ~3 waves of CTAs on the weight stream.
+static int select_splitk_config(int64_t M, int64_t N, int64_t K, int num_sms) {
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + 127) / 128);
+  const int64_t k_blocks = (K + BK - 1) / BK;
+  // Measured on B200 (M=16 and 128, N=14336, K=4096, cold L2): the split rows are 10-50 % SLOWER than
+  // the plain 128x128 row (26.6 vs 29.7 us and 24.6 vs 37.9 us), so the automatic choice does not use
+  // them yet; they stay in the table for explicit selection.
+  constexpr bool kAutoSplitK = false;
+  if (!kAutoSplitK || M > BM || tiles >= num_sms || k_blocks < 8) return -1;
+  const int64_t want = (3 * num_sms + tiles - 1) / tiles;
+  int splits = 2;
+  while (splits < 8 && splits < want) splits *= 2;
+  while (splits > 2 && k_blocks / splits < 4) splits /= 2;
+  return splits == 2 ? 11 : (splits == 4 ? 12 : 13);
+}
+
+int gemm_select_config(int64_t M, int64_t N, int64_t K, bool y_colmajor, int out_dtype, int num_sms) {
+  (void)out_dtype;
+  const int split_cfg = select_splitk_config(M, N, K, num_sms);
+  if (split_cfg >= 0) return split_cfg;
+  return gemm_select_config_nosplit(M, N, K, y_colmajor, num_sms);
+}
+
 int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
   int cfg_id = a.cfg_id;
-  if (cfg_id < 0) cfg_id = gemm_select_config(a.M, a.N, a.K, a.y_colmajor, a.out_dtype, ctx->num_sms);
+  if (cfg_id < 0) {
+    cfg_id = gemm_select_config(a.M, a.N, a.K, a.y_colmajor, a.out_dtype, ctx->num_sms);
+    // The table's split-K rows need scratch; a caller that passed none gets the best row without.
+    if (kGemmConfigs[cfg_id].splits > 1 &&
+        (a.workspace == nullptr || a.workspace_bytes < gemm_workspace_bytes(a.M, a.N, a.K, a.out_dtype, cfg_id))) {
+      cfg_id = gemm_select_config_nosplit(a.M, a.N, a.K, a.y_colmajor, ctx->num_sms);
+    }
+  }
   if (cfg_id >= kNumGemmConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: no such config");
   const GemmConfig& c = kGemmConfigs[cfg_id];
   if (!a.y_colmajor && c.bn < 128) {
@@ -654,7 +768,7 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
       case 256:
         return launch_by_dtype<256, 4, false>(a, ctx, ta, tb, c.group_m);
       case 128:
-        return launch_by_dtype<128, 6, false>(a, ctx, ta, tb, c.group_m);
+        return launch_by_dtype<128, 6, false>(a, ctx, ta, tb, c.group_m, c.splits);
       case 64:
         return launch_by_dtype<64, 8, false>(a, ctx, ta, tb, c.group_m);
     }
@@ -663,7 +777,7 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
       case 256:
         return launch_by_dtype<256, 4, true>(a, ctx, ta, tb, c.group_m);
       case 128:
-        return launch_by_dtype<128, 6, true>(a, ctx, ta, tb, c.group_m);
+        return launch_by_dtype<128, 6, true>(a, ctx, ta, tb, c.group_m, c.splits);
     }
   }
   return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: config has no kernel instance");

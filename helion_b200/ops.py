@@ -78,11 +78,16 @@ def fp8_gemm(
     if k == 0:
         return out.zero_()
     lib = _lib.load()
+    cfg = -1 if config is None else int(config)
+    # Split-K rows of the tile table need scratch for their fp32 partial sums; like `out` it comes
+    # from torch's caching allocator and is only used by this call's two kernels on this stream.
+    ws_bytes = lib.hb200_fp8_gemm_workspace_bytes(m, n, k, _OUT_DT[out_dtype], cfg)
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
     code = lib.hb200_fp8_gemm(
         x.data_ptr(), y.data_ptr(), out.data_ptr(), m, n, k,
         x.stride(0), x.stride(1), y.stride(0), y.stride(1), out.stride(0),
-        _OUT_DT[out_dtype], -1 if config is None else int(config),
-        None, 0, dev, _stream_ptr(dev),
+        _OUT_DT[out_dtype], cfg,
+        workspace.data_ptr() if workspace is not None else None, ws_bytes, dev, _stream_ptr(dev),
     )
     _lib.raise_for(code, "fp8_gemm")
     return out

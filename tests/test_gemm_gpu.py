@@ -98,6 +98,40 @@ def test_every_table_config_gives_the_same_result(hb):
         hb.fp8_gemm(to_dev(x), to_dev(y.contiguous()), config=2)
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 512, 1024), (16, 14336, 4096), (128, 1024, 2048), (100, 272, 1152)])
+@pytest.mark.parametrize("colmajor", [True, False], ids=["y_colmajor", "y_rowmajor"])
+def test_split_k_configs_match_oracle(hb, m, n, k, colmajor):
+    """Skinny problems run split-K: fp32 partial tiles in scratch memory, then a reduce pass."""
+    from helion_b200 import _lib
+
+    x, y = o.gemm_inputs(m, n, k, seed=77 + m + n)
+    if not colmajor:
+        y = y.contiguous()
+    base, _ = check_against_oracle(hb, x, y, torch.float32, config=1)
+    for cfg in (None, 11, 12, 13):
+        for dt in (torch.float32, torch.bfloat16, torch.float16):
+            got, _ = check_against_oracle(hb, x, y, dt, config=cfg)
+        np.testing.assert_allclose(got, o.round_to_dtype(base, "fp16"), rtol=2e-3, atol=2e-2)
+
+
+def test_split_k_needs_its_workspace(hb):
+    from helion_b200 import _lib
+
+    lib = _lib.load()
+    x, y = o.gemm_inputs(16, 512, 1024, seed=3)
+    xd, yd = to_dev(x), to_dev(y)
+    out = torch.empty(16, 512, dtype=torch.float16, device="cuda")
+    assert lib.hb200_fp8_gemm_workspace_bytes(16, 512, 1024, _lib.DT_FP16, 12) == 4 * 16 * 512 * 4
+    args = (xd.data_ptr(), yd.data_ptr(), out.data_ptr(), 16, 512, 1024, 1024, 1, 1, 1024, 512, _lib.DT_FP16)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.hb200_fp8_gemm(*args, 12, None, 0, 0, stream) == _lib.ERR_WORKSPACE  # explicit split-K row
+    assert "workspace" in _lib.last_error()
+    assert lib.hb200_fp8_gemm(*args, -1, None, 0, 0, stream) == 0  # the automatic choice never needs scratch
+    torch.cuda.synchronize()
+    want = o.fp8_gemm(o.torch_fp8_to_bits(x), o.torch_fp8_to_bits(y), "fp16")
+    np.testing.assert_allclose(out.float().cpu().numpy(), want, rtol=2e-2, atol=2e-2)
+
+
 def test_weight_like_operand_and_large_magnitudes(hb):
     x, w = o.gemm_inputs(64, 256, 512, seed=6, weight_like=True)  # max |w| = 448
     got, want = check_against_oracle(hb, x, w, torch.float32)

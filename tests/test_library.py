@@ -39,6 +39,12 @@ def test_config_table_is_described(built_library):
     for i in range(n):
         assert f"gemm cfg {i}" in _lib.describe_config(_lib.OP_GEMM, i)
     assert _lib.num_configs(_lib.OP_ATTENTION) >= 1
+    # split-K rows say how much scratch they need; the others need none
+    lib = built_library
+    assert lib.hb200_fp8_gemm_workspace_bytes(16, 14336, 4096, _lib.DT_BF16, 12) == 4 * 16 * 14336 * 4
+    assert lib.hb200_fp8_gemm_workspace_bytes(8192, 8192, 8192, _lib.DT_BF16, -1) == 0
+    assert lib.hb200_fp8_gemm_workspace_bytes(16, 14336, 4096, _lib.DT_BF16, -1) == 0  # automatic choice: no scratch
+    assert lib.hb200_fp8_gemm_workspace_bytes(16, 14336, 4096, _lib.DT_BF16, 0) == 0
     with pytest.raises(ValueError):
         _lib.describe_config(_lib.OP_GEMM, 10_000)
 
