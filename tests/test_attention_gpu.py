@@ -124,7 +124,8 @@ def test_matches_reference_golden_outputs(hb, name):
     q = torch.from_numpy(z["q"]).cuda().view(torch.float8_e4m3fn)
     k = torch.from_numpy(z["k"]).cuda().view(torch.float8_e4m3fn)
     v = torch.from_numpy(z["v_sd"]).cuda().view(torch.float8_e4m3fn).permute(0, 2, 1)
-    assert tuple(v.stride()) == tuple(int(s) for s in z["v_strides"])  # the layout the reference ran on
+    # the layout the reference ran on (the stride of a size-1 leading dimension is arbitrary)
+    assert tuple(v.stride())[1:] == tuple(int(s) for s in z["v_strides"])[1:]
     out = hb.fp8_attention(q, k, v, batch, heads)  # the reference's call
     got, want = bits(out), z["out"]
     gf, wf = o.e4m3_decode(got), o.e4m3_decode(want)
