@@ -26,6 +26,7 @@ ERR_WORKSPACE = -9
 
 DT_FP16, DT_BF16, DT_FP32, DT_E4M3 = 0, 1, 2, 3
 OP_GEMM, OP_ATTENTION = 0, 1
+STATIC_SCRATCH_BYTES = 4 << 20
 
 # Every symbol the header declares, with (restype, argtypes).
 _i64 = ctypes.c_int64
@@ -36,6 +37,10 @@ SIGNATURES = {
         ctypes.c_int,
         [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.c_int, ctypes.c_int, _vp,
          ctypes.c_size_t, ctypes.c_int, _vp],
+    ),
+    "hb200_fp8_gemm_splitk_static": (
+        ctypes.c_int,
+        [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp],
     ),
     "hb200_fp8_gemm_workspace_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, ctypes.c_int, ctypes.c_int]),
     "hb200_fp8_gemm_select_config": (ctypes.c_int, [_i64, _i64, _i64, ctypes.c_int, ctypes.c_int]),

@@ -90,6 +90,19 @@ DeviceCtx* get_device_ctx(int device) {
   return &c;
 }
 
+int ensure_tmap_encoder() {
+  std::lock_guard<std::mutex> lock(g_ctx_mutex);
+  if (g_encode_tiled != nullptr) return HB200_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || fn == nullptr || qres != cudaDriverEntryPointSuccess) {
+    return set_error(HB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  }
+  g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  return HB200_OK;
+}
+
 int device_init_error(int device) {
   if (device >= 0 && device < kMaxDevices && g_ctx[device].init_error != 0) return g_ctx[device].init_error;
   return HB200_ERR_CUDA;
@@ -244,6 +257,71 @@ int hb200_fp8_gemm(const void* x, const void* y, void* out, int64_t M, int64_t N
   a.stream = static_cast<cudaStream_t>(stream);
   DeviceGuard guard(device);
   return launch_fp8_gemm(a, ctx);
+}
+
+int hb200_fp8_gemm_splitk_static(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K,
+                                 int64_t x_rs, int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs, int out_dtype,
+                                 int splits, int device, void* stream) {
+  // Same argument contract as hb200_fp8_gemm, checked here again so that this entry point shares no
+  // code path with it before the launch.
+  if (out_dtype != HB200_DT_FP16 && out_dtype != HB200_DT_BF16 && out_dtype != HB200_DT_FP32) {
+    return set_error(HB200_ERR_BAD_DTYPE, "fp8_gemm_splitk_static: out_dtype must be FP16, BF16 or FP32");
+  }
+  if (M < 1 || N < 1 || K < 1 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) {
+    return set_error(HB200_ERR_BAD_SHAPE, "fp8_gemm_splitk_static: M, N, K must be in [1, 2^31)");
+  }
+  if (K % 16 != 0 || N % 8 != 0) {
+    return set_error(HB200_ERR_BAD_SHAPE, "fp8_gemm_splitk_static: K must be a multiple of 16 and N of 8");
+  }
+  if (splits < 2 || splits > 8) return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm_splitk_static: splits must be 2..8");
+  if (x == nullptr || y == nullptr || out == nullptr) {
+    return set_error(HB200_ERR_ALIGN, "fp8_gemm_splitk_static: null pointer");
+  }
+  if (x_cs != 1 || x_rs < K || x_rs % 16 != 0) {
+    return set_error(HB200_ERR_BAD_STRIDE, "fp8_gemm_splitk_static: x must be row-major with a row stride >= K, multiple of 16");
+  }
+  bool y_colmajor;
+  int64_t ldb;
+  if (y_rs == 1 && (K == 1 || y_cs >= K)) {
+    y_colmajor = true;
+    ldb = y_cs;
+  } else if (y_cs == 1 && y_rs >= N && N % 16 == 0) {
+    y_colmajor = false;
+    ldb = y_rs;
+  } else {
+    return set_error(HB200_ERR_BAD_STRIDE,
+                     "fp8_gemm_splitk_static: y must be column-major, or row-major with N a multiple of 16");
+  }
+  if (ldb % 16 != 0) {
+    return set_error(HB200_ERR_BAD_STRIDE, "fp8_gemm_splitk_static: y leading stride must be a multiple of 16");
+  }
+  const int64_t out_elem = out_dtype == HB200_DT_FP32 ? 4 : 2;
+  if (out_rs < N || (out_rs * out_elem) % 16 != 0) {
+    return set_error(HB200_ERR_BAD_STRIDE, "fp8_gemm_splitk_static: out rows must be >= N long and 16-byte aligned");
+  }
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out)) & 15u) {
+    return set_error(HB200_ERR_ALIGN, "fp8_gemm_splitk_static: x, y and out must be 16-byte aligned");
+  }
+  if (device < 0 || device >= kMaxDevices) return set_error(HB200_ERR_CUDA, "device index out of range");
+  GemmArgs a;
+  a.x = x;
+  a.y = y;
+  a.out = out;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.lda = x_rs;
+  a.ldb = ldb;
+  a.y_colmajor = y_colmajor;
+  a.ldc = out_rs;
+  a.out_dtype = out_dtype;
+  a.cfg_id = -1;
+  a.workspace = nullptr;  // filled in by the launcher with the static array's address
+  a.workspace_bytes = 0;
+  a.device = device;
+  a.stream = static_cast<cudaStream_t>(stream);
+  DeviceGuard guard(device);
+  return launch_fp8_gemm_static_scratch(a, splits);
 }
 
 int hb200_fp8_attention(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S, int64_t D,

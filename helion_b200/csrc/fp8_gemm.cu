@@ -16,6 +16,8 @@
 // (B operand MN-major); both are fed straight from TMA without a transpose pass.
 #include <algorithm>
 #include <cstdio>
+#include <mutex>
+#include <string>
 
 #include "common.cuh"
 #include "host.h"
@@ -715,6 +717,87 @@ int gemm_select_config(int64_t M, int64_t N, int64_t K, bool y_colmajor, int out
   const int split_cfg = select_splitk_config(M, N, K, num_sms);
   if (split_cfg >= 0) return split_cfg;
   return gemm_select_config_nosplit(M, N, K, y_colmajor, num_sms);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Split-K with the partial sums in a fixed device array (hb200_fp8_gemm_splitk_static): for callers
+// that must not allocate.  The array's NAME is only a host-side handle; its device address is
+// looked up once per device with cudaGetSymbolAddress and that pointer is what the kernels get.
+// Every call on a device uses the same array, so calls that can overlap on the GPU race on it.
+// Nothing has to be cleared between calls: each (split, row < M, column < N) element is written by
+// exactly one CTA of the first kernel before the reduce kernel reads it.
+// ------------------------------------------------------------------------------------------------
+namespace {
+static __device__ __align__(256) float g_splitk_static_scratch[HB200_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+struct StaticScratchState {
+  bool ready = false;
+  float* scratch = nullptr;  // device address of g_splitk_static_scratch on this device
+  int num_sms = 0;
+};
+StaticScratchState g_static_state[64];
+std::mutex g_static_mutex;
+}  // namespace
+
+int launch_fp8_gemm_static_scratch(const GemmArgs& a_in, int splits_requested) {
+  const int splits = effective_splits(a_in.K, splits_requested);
+  if (splits < 2) {
+    return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm_splitk_static: K is too short to split (needs at least 2 blocks of 128)");
+  }
+  const size_t need = static_cast<size_t>(splits) * a_in.M * a_in.N * sizeof(float);
+  if (need > HB200_STATIC_SCRATCH_BYTES) {
+    return set_error(HB200_ERR_WORKSPACE,
+                     "fp8_gemm_splitk_static: splits*M*N*4 = " + std::to_string(need) + " bytes exceeds the static scratch of " +
+                         std::to_string(HB200_STATIC_SCRATCH_BYTES) + " bytes; use hb200_fp8_gemm with a workspace");
+  }
+  StaticScratchState* st = &g_static_state[a_in.device];
+  {
+    // First call on this device (the device is current here): resolve the array's device address.
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!st->ready) {
+      int major = 0, sms = 0;
+      HB_CUDA_CHECK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, a_in.device));
+      HB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, a_in.device));
+      if (major != 10) return set_error(HB200_ERR_UNSUPPORTED_ARCH, "this library holds sm_100a code only");
+      void* ptr = nullptr;
+      HB_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_splitk_static_scratch));
+      int rc = ensure_tmap_encoder();
+      if (rc != HB200_OK) return rc;
+      st->scratch = static_cast<float*>(ptr);
+      st->num_sms = sms;
+      st->ready = true;
+    }
+  }
+  GemmArgs a = a_in;
+  a.workspace = st->scratch;
+  a.workspace_bytes = HB200_STATIC_SCRATCH_BYTES;
+  DeviceCtx ctx;  // only the fields the launcher reads; no status word (a wait that runs out still aborts the kernel)
+  ctx.initialised = true;
+  ctx.num_sms = st->num_sms;
+  ctx.status_dev = nullptr;
+
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(a.lda)};
+    const uint32_t box[2] = {BK, BM};
+    int rc = encode_tmap_u8(&ta, a.x, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB200_OK) return rc;
+  }
+  if (a.y_colmajor) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.N)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(a.ldb)};
+    const uint32_t box[2] = {BK, 128};
+    int rc = encode_tmap_u8(&tb, a.y, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB200_OK) return rc;
+    return launch_by_dtype<128, 6, false>(a, &ctx, ta, tb, 8, splits);
+  }
+  const uint64_t dims[2] = {static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K)};
+  const uint64_t strides[1] = {static_cast<uint64_t>(a.ldb)};
+  const uint32_t box[2] = {128, BK};
+  int rc = encode_tmap_u8(&tb, a.y, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != HB200_OK) return rc;
+  return launch_by_dtype<128, 6, true>(a, &ctx, ta, tb, 8, splits);
 }
 
 int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {

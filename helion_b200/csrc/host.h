@@ -86,6 +86,11 @@ int gemm_describe_config(int cfg_id, char* buf, int buf_len);
 int gemm_select_config(int64_t M, int64_t N, int64_t K, bool y_colmajor, int out_dtype, int num_sms);
 size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int cfg_id);
 
+// Split-K launch whose partial sums live in the library's static device array (no allocation).
+int launch_fp8_gemm_static_scratch(const GemmArgs& args, int splits);
+// Makes the tensor-map encoder available without creating a device context (no allocation).
+int ensure_tmap_encoder();
+
 struct AttnArgs {
   const void* q;
   const void* k;

@@ -96,6 +96,30 @@ HB200_API int hb200_fp8_attention(const void* q, const void* k, const void* v, v
                         const int64_t out_strides[3], float scale_log2, int out_dtype, int cfg_id, int device,
                         void* stream);
 
+/* Split-K FP8 GEMM that allocates nothing: same computation and arguments as hb200_fp8_gemm with a
+ * split-K row of the table, but the fp32 partial sums live in a fixed array compiled into the
+ * library instead of a caller-provided workspace.  It has no counterpart in the reference; it
+ * exists for callers that must not call cudaMalloc / cudaFree (or torch's allocator) around a GEMM:
+ * a serving loop whose device memory was handed out completely at start-up, an operator hook that
+ * runs inside another runtime which owns the allocator, or a host callback where the device-wide
+ * synchronisation that an allocation can cause would stall unrelated streams.
+ *   - scratch: HB200_STATIC_SCRATCH_BYTES of device memory per GPU that loads the library, held
+ *     until the process exits; a call needs splits * M * N * 4 bytes of it and is rejected with
+ *     HB200_ERR_WORKSPACE when that exceeds the array (use hb200_fp8_gemm with a workspace then);
+ *   - splits: 2..8 (the K range is cut into that many parts; every part of every output element is
+ *     written before it is read, so the array needs no clearing between calls);
+ *   - the first call on a device looks up the array's device address (no allocation); make that
+ *     first call before starting any stream capture;
+ *   - all calls on a device share the one array: two calls whose kernels can overlap on the GPU
+ *     (different streams, no dependency between them) race on it and give wrong results -- order them;
+ *   - calls neither cudaMalloc nor cudaFree nor any allocating library routine; launches two kernels
+ *     (partial products, then the ordered sum and conversion) on the given stream.
+ * x, y, out, sizes, strides, out_dtype and the return codes are those of hb200_fp8_gemm. */
+#define HB200_STATIC_SCRATCH_BYTES (4u << 20)
+HB200_API int hb200_fp8_gemm_splitk_static(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K,
+                                           int64_t x_rs, int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs,
+                                           int out_dtype, int splits, int device, void* stream);
+
 /* Tile-config table introspection (the table replaces Helion's autotuner,
  * helion/autotuner/differential_evolution.py:20-101). */
 HB200_API int hb200_num_configs(int op);
