@@ -187,7 +187,7 @@ def aten_scaled_mm_cpu_gflops():
         return None
 
 
-def run_reference(args, rank: int) -> None:
+def run_reference(args, rank: int, emit) -> None:
     if rank != 0:
         return
     import torch
@@ -220,7 +220,7 @@ def run_reference(args, rank: int) -> None:
                          "aten_scaled_mm_cpu_gflops_256": aten_scaled_mm_cpu_gflops()},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def main() -> None:
@@ -237,9 +237,19 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    # Libraries (NCCL's version banner, for one) write to stdout; keep stdout for the one JSON line by
+    # pointing file descriptor 1 at stderr until that line is printed.
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj) -> None:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        print(json.dumps(obj), flush=True)
 
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, emit)
         return
 
     import torch
@@ -254,7 +264,7 @@ def main() -> None:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if args.only is not None:
-        run_only(args, torch, dev, hb, _lib)
+        run_only(args, torch, dev, hb, _lib, emit)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
@@ -409,7 +419,7 @@ def main() -> None:
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch from the committed ncu summary
@@ -462,7 +472,7 @@ def make_workload(name: str, torch, dev, hb, config=None):
 WORKLOADS = ["gemm_8192", *ATTN_SHAPES, *(f"mlp_M{m}" for m in MLP_M), "cublaslt_8192"]
 
 
-def run_only(args, torch, dev, hb, _lib) -> None:
+def run_only(args, torch, dev, hb, _lib, emit) -> None:
     """`--only NAME`: time one named workload (used for sweeps and as the command under ncu)."""
     fn, flops, byts = make_workload(args.only, torch, dev, hb, args.config)
     flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
@@ -470,8 +480,8 @@ def run_only(args, torch, dev, hb, _lib) -> None:
     torch.cuda.synchronize()
     _lib.check_status(dev.index)
     med = statistics.median(ts)
-    print(json.dumps({"only": args.only, "config": args.config, "steps": args.steps, "ms": med, "ms_min": min(ts),
-                      "tflops": flops / (med * 1e-3) / 1e12, "gbs": byts / (med * 1e-3) / 1e9}), flush=True)
+    emit({"only": args.only, "config": args.config, "steps": args.steps, "ms": med, "ms_min": min(ts),
+          "tflops": flops / (med * 1e-3) / 1e12, "gbs": byts / (med * 1e-3) / 1e9})
 
 
 def run_extras(hb, _lib, o, torch, dev, flush, fp8_peak, peaks) -> dict:
