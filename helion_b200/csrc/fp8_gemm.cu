@@ -525,6 +525,263 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 }
 
 // ------------------------------------------------------------------------------------------------
+// CTA-pair variant with 256 x 256 outputs per CTA (512 x 256 per pair).  Each CTA keeps 256 rows of
+// x and 128 columns of y per K block in shared memory and feeds TWO M = 256 UMMAs per K step from
+// them (rows [0,128) of both CTAs -> accumulator 0, rows [128,256) -> accumulator 1), so the y tile
+// is loaded once for twice the outputs: 48 KB per CTA per 128-deep K block for 256 x 256 outputs,
+// a quarter less L2->SM traffic per flop than the 256 x 256 pair tile.  The two accumulators fill
+// all 512 tensor-memory columns, so the epilogue cannot overlap the next tile's MMAs; instead eight
+// epilogue warps drain the two accumulators in parallel and each accumulator is handed back on its
+// own barrier, and the producer keeps prefetching the next tile's stages meanwhile.
+// ------------------------------------------------------------------------------------------------
+template <int STAGES>
+struct Pair2Layout {
+  static constexpr int A_BYTES = 256 * BK;  // 256 rows of x (two 128-row MMA operands)
+  static constexpr int B_BYTES = 128 * BK;  // 128 of the tile's 256 columns of y
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  // full[ST] empty[ST] acc_full[1] acc_empty[2] drain[1]
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  // epilogue staging: per epilogue warp 4 KB (two 32-row x 64-byte buffers for 16-bit outputs, one
+  // 32-row x 128-byte buffer for fp32), written swizzled and drained by TMA stores
+  static constexpr int EPI_OFFSET = RING_BYTES;
+  static constexpr int EPI_BYTES = 8 * 4096;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_BYTES;
+  static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;
+  static constexpr int SMEM_BYTES = MISC_OFFSET + 16 + 1024;
+  static constexpr int TMEM_COLS = 512;
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+};
+
+constexpr int PAIR2_BM = 512;
+constexpr int PAIR2_BN = 256;
+constexpr int PAIR2_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
+
+template <int STAGES, bool B_MN_MAJOR, int OUT_DT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR2_THREADS, 1)
+fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_out, int M, int N, int K, int group_m,
+                      uint32_t* status) {
+  using L = Pair2Layout<STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* full = bars;                       // used in the leader only
+  uint64_t* empty = bars + STAGES;             // one set per CTA
+  uint64_t* acc_full = bars + 2 * STAGES;      // one per CTA: both accumulators of the tile are complete
+  uint64_t* acc_empty = bars + 2 * STAGES + 1; // [2] used in the leader only (8 arrivals each: 4 warps x 2 CTAs)
+  uint64_t* drain = bars + 2 * STAGES + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFFSET + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int m_tiles = (M + PAIR2_BM - 1) / PAIR2_BM;
+  const int n_tiles = (N + PAIR2_BN - 1) / PAIR2_BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + BK - 1) / BK;
+  const WaitCtx wctx{abort_flag, status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(&acc_empty[0], 8);
+    mbar_init(&acc_empty[1], 8);
+    mbar_init(drain, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, L::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) --------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, group_m);
+        const int row0 = tc.m_blk * PAIR2_BM + static_cast<int>(rank) * 256;
+        const int col0 = tc.n_blk * PAIR2_BN + static_cast<int>(rank) * 128;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u, wctx, SITE_GEMM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + s * L::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + L::A_BYTES;
+          const uint32_t full_leader = map_to_cta(smem_u32(&full[s]), 0);
+          if (leader) mbar_arrive_expect_tx(&full[s], 2 * L::STAGE_BYTES);
+          tma_load_2d_pair(a_dst, &tmap_a, full_leader, kb * BK, row0);  // box: 128 bytes x 256 rows
+          if constexpr (!B_MN_MAJOR) {
+            tma_load_2d_pair(b_dst, &tmap_b, full_leader, kb * BK, col0);
+          } else {
+            tma_load_2d_pair(b_dst, &tmap_b, full_leader, col0, kb * BK);
+          }
+        }
+      }
+      if (!ok && leader) {
+        const uint32_t back = it < static_cast<uint32_t>(STAGES) ? it : static_cast<uint32_t>(STAGES);
+        for (uint32_t j = it - back; j < it; ++j) mbar_drain(&full[j % STAGES], (j / STAGES) & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader CTA only) -----------------------------
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_e4m3(256, PAIR2_BN, false, B_MN_MAJOR);
+      uint32_t it = 0;
+      uint32_t tile_iter = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++tile_iter) {
+        const uint32_t free_parity = (tile_iter & 1u) ^ 1u;
+        for (int kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&full[s], ph, wctx, SITE_GEMM_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + L::A_BYTES;
+          const uint64_t b_desc = B_MN_MAJOR ? make_smem_desc(b_addr, 1024, 1024, SWZ_128B)
+                                             : make_smem_desc(b_addr, 16, 1024, SWZ_128B);
+          // accumulator by accumulator, so that in the first K block of a tile the MMAs into
+          // accumulator 0 can start while the epilogue still drains accumulator 1
+#pragma unroll
+          for (int acc = 0; acc < 2; ++acc) {
+            if (kb == 0) {
+              if (!mbar_wait(&acc_empty[acc], free_parity, wctx, SITE_GEMM_ACC_EMPTY)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+            }
+            const uint64_t a_desc = make_smem_desc(a_addr + acc * (128 * BK), 16, 1024, SWZ_128B);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t ad = desc_advance(a_desc, k * UMMA_K);
+              const uint64_t bd = desc_advance(b_desc, B_MN_MAJOR ? k * UMMA_K * 128 : k * UMMA_K);
+              umma_f8_ss_pair(tmem_base + acc * PAIR2_BN, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+          }
+          if (!ok) break;
+          const uint32_t e_local = smem_u32(&empty[s]);
+          umma_commit_pair(e_local);
+          umma_commit_pair(map_to_cta(e_local, 1));
+        }
+        if (ok) {
+          const uint32_t f_local = smem_u32(acc_full);
+          umma_commit_pair(f_local);
+          umma_commit_pair(map_to_cta(f_local, 1));
+        }
+      }
+      if (!ok) {
+        umma_commit_pair(smem_u32(drain));
+        mbar_drain(drain, 0);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- epilogue (both CTAs, 8 warps) ----------------------------
+    // Each warp moves its 32 rows x 256 columns in 32-column chunks: tcgen05.ld -> convert -> swizzled
+    // st.shared into a staging buffer -> one TMA store of the 32 x 32 block (which also clips rows
+    // beyond M and columns beyond N).  Stores stay in flight while the next chunk is converted.
+    constexpr bool OUT32 = OUT_DT == HB200_DT_FP32;
+    constexpr int ROW_BYTES = OUT32 ? 128 : 64;       // bytes of one staged row (32 columns)
+    constexpr int STG_BYTES = 32 * ROW_BYTES;         // one staging buffer
+    constexpr int NBUF = OUT32 ? 1 : 2;
+    const int quarter = warp & 3;
+    const int acc = (warp - 2) >> 2;  // warps 2-5 drain accumulator 0, warps 6-9 accumulator 1
+    uint8_t* stage = smem + L::EPI_OFFSET + (warp - 2) * 4096;
+    // 16-byte chunk j of row r lives at chunk j ^ ((r >> 1) & 3) (64-byte rows, SWIZZLE_64B) or
+    // j ^ (r & 7) (128-byte rows, SWIZZLE_128B): the pattern the output tensor map expects
+    const uint32_t swz = OUT32 ? static_cast<uint32_t>(lane & 7) : static_cast<uint32_t>((lane >> 1) & 3);
+    uint32_t chunk_count = 0;
+    uint32_t tile_iter = 0;
+    for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++tile_iter) {
+      const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, group_m);
+      bool ok = mbar_wait(acc_full, tile_iter & 1u, wctx, SITE_GEMM_ACC_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row0 = tc.m_blk * PAIR2_BM + static_cast<int>(rank) * 256 + acc * 128 + quarter * 32;
+      const uint32_t t_row = tmem_base + acc * PAIR2_BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 2
+      for (int c = 0; c < PAIR2_BN; c += 32, ++chunk_count) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c, r);
+        tmem_wait_ld();
+        uint8_t* buf = stage + (chunk_count % NBUF) * STG_BYTES;
+        // the TMA store that last read this buffer must be done with it
+        if (lane == 0) tma_store_wait_read<NBUF - 1>();
+        __syncwarp();
+        uint8_t* dst_row = buf + lane * ROW_BYTES;
+        if constexpr (OUT32) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            *reinterpret_cast<uint4*>(dst_row + ((static_cast<uint32_t>(j) ^ swz) << 4)) =
+                make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t p[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float lo = __uint_as_float(r[8 * j + 2 * q]);
+              const float hi = __uint_as_float(r[8 * j + 2 * q + 1]);
+              p[q] = (OUT_DT == HB200_DT_BF16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+            }
+            *reinterpret_cast<uint4*>(dst_row + ((static_cast<uint32_t>(j) ^ swz) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          // blocks that lie wholly outside the matrix are not stored at all (partial ones are clipped)
+          if (row0 < M && tc.n_blk * PAIR2_BN + c < N) tma_store_2d(&tmap_out, buf, tc.n_blk * PAIR2_BN + c, row0);
+          tma_store_commit();
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+    }
+    if (lane == 0) tma_store_wait<0>();  // all output blocks written before the CTA exits
+  }
+
+  // ------------------------------- teardown ----------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, L::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // tile-config table
 // ------------------------------------------------------------------------------------------------
 struct GemmConfig {
@@ -551,6 +808,10 @@ const GemmConfig kGemmConfigs[] = {
     {128, 6, 8, false, 2, "1 CTA, 128x128x128 tiles, split-K 2: skinny M, HBM-bound"},
     {128, 6, 8, false, 4, "1 CTA, 128x128x128 tiles, split-K 4: skinny M, HBM-bound"},
     {128, 6, 8, false, 8, "1 CTA, 128x128x128 tiles, split-K 8: skinny M, HBM-bound"},
+    {512, 4, 8, true, 1, "CTA pair, 512x256x128 tiles (256x256 per CTA, two accumulators), 4 stages, group_m 8"},
+    {512, 4, 4, true, 1, "CTA pair, 512x256x128 tiles (256x256 per CTA, two accumulators), 4 stages, group_m 4"},
+    {512, 4, 2, true, 1, "CTA pair, 512x256x128 tiles (256x256 per CTA, two accumulators), 4 stages, group_m 2"},
+    {512, 4, 16, true, 1, "CTA pair, 512x256x128 tiles (256x256 per CTA, two accumulators), 4 stages, group_m 16"},
 };
 constexpr int kNumGemmConfigs = sizeof(kGemmConfigs) / sizeof(kGemmConfigs[0]);
 
@@ -572,6 +833,51 @@ int launch_pair_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& t
                                                               group_m, ctx->status_dev);
   HB_CUDA_CHECK(cudaGetLastError());
   return HB200_OK;
+}
+
+template <bool B_MN, int OUT_DT>
+int launch_pair2_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
+  using L = Pair2Layout<4>;
+  auto kernel = fp8_gemm_pair2_kernel<4, B_MN, OUT_DT>;
+  static bool attr_set[64] = {};
+  if (!attr_set[a.device]) {
+    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
+    attr_set[a.device] = true;
+  }
+  const int64_t m_tiles = (a.M + PAIR2_BM - 1) / PAIR2_BM;
+  const int64_t n_tiles = (a.N + PAIR2_BN - 1) / PAIR2_BN;
+  const int pairs = static_cast<int>(std::min<int64_t>(m_tiles * n_tiles, ctx->num_sms / 2));
+  // output map: 32 x 32 element boxes, swizzled like the staging buffers the epilogue writes
+  CUtensorMap tout;
+  {
+    constexpr bool out32 = OUT_DT == HB200_DT_FP32;
+    const uint64_t elem = out32 ? 4 : 2;
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(a.ldc) * elem};
+    const uint32_t box[2] = {32, 32};
+    int rc = encode_tmap(&tout, out32 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, a.out, 2, dims,
+                         strides, box, out32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc != HB200_OK) return rc;
+  }
+  kernel<<<2 * pairs, PAIR2_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, tout, static_cast<int>(a.M),
+                                                                static_cast<int>(a.N), static_cast<int>(a.K), group_m,
+                                                                ctx->status_dev);
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB200_OK;
+}
+
+template <bool B_MN>
+int launch_pair2_by_dtype(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
+  switch (a.out_dtype) {
+    case HB200_DT_FP16:
+      return launch_pair2_instance<B_MN, HB200_DT_FP16>(a, ctx, ta, tb, group_m);
+    case HB200_DT_BF16:
+      return launch_pair2_instance<B_MN, HB200_DT_BF16>(a, ctx, ta, tb, group_m);
+    case HB200_DT_FP32:
+      return launch_pair2_instance<B_MN, HB200_DT_FP32>(a, ctx, ta, tb, group_m);
+    default:
+      return set_error(HB200_ERR_BAD_DTYPE, "fp8_gemm: unsupported out_dtype");
+  }
 }
 
 template <int STAGES, bool B_MN>
@@ -655,7 +961,8 @@ int gemm_describe_config(int cfg_id, char* buf, int buf_len) {
   if (cfg_id < 0 || cfg_id >= kNumGemmConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: no such config");
   const GemmConfig& c = kGemmConfigs[cfg_id];
   return std::snprintf(buf, buf_len, "gemm cfg %d: BM=%d BN=%d BK=128 stages=%d group_m=%d split_k=%d (%s)", cfg_id,
-                       c.pair ? 256 : 128, c.bn, c.stages, c.group_m, c.splits, c.note);
+                       c.bn == 512 ? 512 : (c.pair ? 256 : 128), c.bn == 512 ? 256 : c.bn, c.stages, c.group_m, c.splits,
+                       c.note);
 }
 
 size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int cfg_id) {
@@ -820,7 +1127,7 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(a.lda)};
-    const uint32_t box[2] = {BK, BM};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(c.bn == 512 ? 256 : BM)};  // the 512x256 pair tile loads 256 rows per CTA
     int rc = encode_tmap_u8(&ta, a.x, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != HB200_OK) return rc;
   }
@@ -838,6 +1145,10 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
     if (rc != HB200_OK) return rc;
   }
 
+  if (c.pair && c.bn == 512) {
+    return a.y_colmajor ? launch_pair2_by_dtype<false>(a, ctx, ta, tb, c.group_m)
+                        : launch_pair2_by_dtype<true>(a, ctx, ta, tb, c.group_m);
+  }
   if (c.pair) {
     if (c.stages == 6) {
       return a.y_colmajor ? launch_pair_by_dtype<6, false>(a, ctx, ta, tb, c.group_m)
