@@ -422,9 +422,9 @@ def main() -> None:
         emit(line)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch from the committed ncu summary
-# (profiles/); None until a capture exists.
-TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch, from the committed ncu summary
+# profiles/fp8_gemm_kernel_8192.md (331.8 MB read + 115.8 MB written).
+TRAFFIC_BYTES_PER_LAUNCH = 447_563_264
 
 
 ATTN_SHAPES = {"attn_B4_H48_S1024_D64": (4, 48, 1024, 64), "attn_B8_H32_S4096_D128": (8, 32, 4096, 128)}

@@ -96,6 +96,56 @@ __device__ __forceinline__ void store_row_chunk(void* out, int64_t row_offset_el
   }
 }
 
+// Epilogue through shared memory and TMA: one warp stages a 32-row x 32-column block of converted
+// outputs (row = lane) in a swizzled buffer and one lane stores it with a tiled bulk copy, which
+// writes full row segments (instead of 32 scattered 16-byte pieces per store instruction) and clips
+// rows beyond M / columns beyond N.  `stage` holds NBUF buffers of 32 x ROW_BYTES; the store that last
+// used a buffer is waited for (its smem reads only) before the buffer is rewritten.
+template <int OUT_DT>
+struct StagedStore {
+  static constexpr bool OUT32 = OUT_DT == HB200_DT_FP32;
+  static constexpr int ROW_BYTES = OUT32 ? 128 : 64;
+  static constexpr int STG_BYTES = 32 * ROW_BYTES;
+  static constexpr int NBUF = OUT32 ? 1 : 2;  // 4 KB per warp either way
+
+  __device__ static __forceinline__ void store(const uint32_t (&r)[32], uint8_t* stage, uint32_t chunk_count, int lane,
+                                               const CUtensorMap* tmap_out, int col, int row0, bool inside) {
+    uint8_t* buf = stage + (chunk_count % NBUF) * STG_BYTES;
+    if (lane == 0) tma_store_wait_read<NBUF - 1>();
+    __syncwarp();
+    // 16-byte chunk j of row r lives at chunk j ^ ((r >> 1) & 3) (64-byte rows, SWIZZLE_64B) or
+    // j ^ (r & 7) (128-byte rows, SWIZZLE_128B): the pattern the output tensor map expects
+    const uint32_t swz = OUT32 ? static_cast<uint32_t>(lane & 7) : static_cast<uint32_t>((lane >> 1) & 3);
+    uint8_t* dst_row = buf + lane * ROW_BYTES;
+    if constexpr (OUT32) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        *reinterpret_cast<uint4*>(dst_row + ((static_cast<uint32_t>(j) ^ swz) << 4)) =
+            make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t p[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float lo = __uint_as_float(r[8 * j + 2 * q]);
+          const float hi = __uint_as_float(r[8 * j + 2 * q + 1]);
+          p[q] = (OUT_DT == HB200_DT_BF16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+        }
+        *reinterpret_cast<uint4*>(dst_row + ((static_cast<uint32_t>(j) ^ swz) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      // blocks that lie wholly outside the matrix are not stored at all (partial ones are clipped)
+      if (inside) tma_store_2d(tmap_out, buf, col, row0);
+      tma_store_commit();
+    }
+  }
+};
+
 template <int BN, int STAGES, bool B_MN_MAJOR, int OUT_DT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, void* out,
@@ -334,7 +384,9 @@ struct PairLayout {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 5;
-  static constexpr int BAR_OFFSET = RING_BYTES;
+  static constexpr int EPI_OFFSET = RING_BYTES;  // 4 KB of output staging per epilogue warp
+  static constexpr int EPI_BYTES = 4 * 4096;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_BYTES;
   static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = MISC_OFFSET + 16 + 1024;
   static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
@@ -347,7 +399,7 @@ constexpr int PAIR_BN = 256;
 template <int STAGES, bool B_MN_MAJOR, int OUT_DT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                     void* out, int M, int N, int K, int64_t ldc, int group_m, uint32_t* status) {
+                     const __grid_constant__ CUtensorMap tmap_out, int M, int N, int K, int group_m, uint32_t* status) {
   using L = PairLayout<STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -488,6 +540,8 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   } else {
     // ------------------------------- epilogue (both CTAs) -------------------------------------
     const int quarter = warp & 3;
+    uint8_t* stage = smem + L::EPI_OFFSET + (warp - 2) * 4096;
+    uint32_t chunk_count = 0;
     uint32_t tile_iter = 0;
     for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++tile_iter) {
       const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, group_m);
@@ -497,21 +551,21 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const int row = tc.m_blk * PAIR_BM + static_cast<int>(rank) * 128 + quarter * 32 + lane;
-      const int64_t row_off = static_cast<int64_t>(row) * ldc;
+      const int row0 = tc.m_blk * PAIR_BM + static_cast<int>(rank) * 128 + quarter * 32;
       const uint32_t t_row = tmem_base + acc * PAIR_BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 2
-      for (int c = 0; c < PAIR_BN; c += 32) {
+      for (int c = 0; c < PAIR_BN; c += 32, ++chunk_count) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_row + c, r);
         tmem_wait_ld();
-        const int col0 = tc.n_blk * PAIR_BN + c;
-        if (row < M && col0 < N) store_row_chunk<OUT_DT>(out, row_off, col0, N, r);
+        const int col = tc.n_blk * PAIR_BN + c;
+        StagedStore<OUT_DT>::store(r, stage, chunk_count, lane, &tmap_out, col, row0, row0 < M && col < N);
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
     }
+    if (lane == 0) tma_store_wait<0>();  // all output blocks written before the CTA exits
   }
 
   // ------------------------------- teardown ----------------------------------------------------
@@ -707,16 +761,9 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     // Each warp moves its 32 rows x 256 columns in 32-column chunks: tcgen05.ld -> convert -> swizzled
     // st.shared into a staging buffer -> one TMA store of the 32 x 32 block (which also clips rows
     // beyond M and columns beyond N).  Stores stay in flight while the next chunk is converted.
-    constexpr bool OUT32 = OUT_DT == HB200_DT_FP32;
-    constexpr int ROW_BYTES = OUT32 ? 128 : 64;       // bytes of one staged row (32 columns)
-    constexpr int STG_BYTES = 32 * ROW_BYTES;         // one staging buffer
-    constexpr int NBUF = OUT32 ? 1 : 2;
     const int quarter = warp & 3;
     const int acc = (warp - 2) >> 2;  // warps 2-5 drain accumulator 0, warps 6-9 accumulator 1
     uint8_t* stage = smem + L::EPI_OFFSET + (warp - 2) * 4096;
-    // 16-byte chunk j of row r lives at chunk j ^ ((r >> 1) & 3) (64-byte rows, SWIZZLE_64B) or
-    // j ^ (r & 7) (128-byte rows, SWIZZLE_128B): the pattern the output tensor map expects
-    const uint32_t swz = OUT32 ? static_cast<uint32_t>(lane & 7) : static_cast<uint32_t>((lane >> 1) & 3);
     uint32_t chunk_count = 0;
     uint32_t tile_iter = 0;
     for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++tile_iter) {
@@ -732,37 +779,8 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_row + c, r);
         tmem_wait_ld();
-        uint8_t* buf = stage + (chunk_count % NBUF) * STG_BYTES;
-        // the TMA store that last read this buffer must be done with it
-        if (lane == 0) tma_store_wait_read<NBUF - 1>();
-        __syncwarp();
-        uint8_t* dst_row = buf + lane * ROW_BYTES;
-        if constexpr (OUT32) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            *reinterpret_cast<uint4*>(dst_row + ((static_cast<uint32_t>(j) ^ swz) << 4)) =
-                make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t p[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float lo = __uint_as_float(r[8 * j + 2 * q]);
-              const float hi = __uint_as_float(r[8 * j + 2 * q + 1]);
-              p[q] = (OUT_DT == HB200_DT_BF16) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
-            }
-            *reinterpret_cast<uint4*>(dst_row + ((static_cast<uint32_t>(j) ^ swz) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
-          }
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          // blocks that lie wholly outside the matrix are not stored at all (partial ones are clipped)
-          if (row0 < M && tc.n_blk * PAIR2_BN + c < N) tma_store_2d(&tmap_out, buf, tc.n_blk * PAIR2_BN + c, row0);
-          tma_store_commit();
-        }
+        const int col = tc.n_blk * PAIR2_BN + c;
+        StagedStore<OUT_DT>::store(r, stage, chunk_count, lane, &tmap_out, col, row0, row0 < M && col < N);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -801,9 +819,9 @@ const GemmConfig kGemmConfigs[] = {
     {256, 4, 4, false, 1, "1 CTA, 128x256x128 tiles, 4 stages, group_m 4"},
     {128, 6, 16, false, 1, "1 CTA, 128x128x128 tiles, 6 stages, group_m 16"},
     {256, 6, 8, true, 1, "CTA pair, 256x256x128 tiles, 6 stages, group_m 8 (of 256-row blocks)"},
-    {256, 7, 8, true, 1, "CTA pair, 256x256x128 tiles, 7 stages, group_m 8"},
-    {256, 7, 4, true, 1, "CTA pair, 256x256x128 tiles, 7 stages, group_m 4"},
-    {256, 7, 16, true, 1, "CTA pair, 256x256x128 tiles, 7 stages, group_m 16"},
+    {256, 6, 12, true, 1, "CTA pair, 256x256x128 tiles, 6 stages, group_m 12"},
+    {256, 6, 2, true, 1, "CTA pair, 256x256x128 tiles, 6 stages, group_m 2"},
+    {256, 6, 16, true, 1, "CTA pair, 256x256x128 tiles, 6 stages, group_m 16"},
     {256, 6, 4, true, 1, "CTA pair, 256x256x128 tiles, 6 stages, group_m 4"},
     {128, 6, 8, false, 2, "1 CTA, 128x128x128 tiles, split-K 2: skinny M, HBM-bound"},
     {128, 6, 8, false, 4, "1 CTA, 128x128x128 tiles, split-K 4: skinny M, HBM-bound"},
@@ -814,6 +832,18 @@ const GemmConfig kGemmConfigs[] = {
     {512, 4, 16, true, 1, "CTA pair, 512x256x128 tiles (256x256 per CTA, two accumulators), 4 stages, group_m 16"},
 };
 constexpr int kNumGemmConfigs = sizeof(kGemmConfigs) / sizeof(kGemmConfigs[0]);
+
+// Output tensor map for the staged epilogue: 32 x 32 element boxes, swizzled like the staging buffers.
+template <int OUT_DT>
+int encode_out_map(CUtensorMap* tout, const GemmArgs& a) {
+  constexpr bool out32 = OUT_DT == HB200_DT_FP32;
+  const uint64_t elem = out32 ? 4 : 2;
+  const uint64_t dims[2] = {static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.M)};
+  const uint64_t strides[1] = {static_cast<uint64_t>(a.ldc) * elem};
+  const uint32_t box[2] = {32, 32};
+  return encode_tmap(tout, out32 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, a.out, 2, dims, strides,
+                     box, out32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+}
 
 template <int STAGES, bool B_MN, int OUT_DT>
 int launch_pair_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
@@ -828,9 +858,14 @@ int launch_pair_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& t
   const int64_t n_tiles = (a.N + PAIR_BN - 1) / PAIR_BN;
   const int64_t num_tiles = m_tiles * n_tiles;
   const int pairs = static_cast<int>(std::min<int64_t>(num_tiles, ctx->num_sms / 2));
-  kernel<<<2 * pairs, NUM_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, a.out, static_cast<int>(a.M),
-                                                              static_cast<int>(a.N), static_cast<int>(a.K), a.ldc,
-                                                              group_m, ctx->status_dev);
+  CUtensorMap tout;
+  {
+    int rc = encode_out_map<OUT_DT>(&tout, a);
+    if (rc != HB200_OK) return rc;
+  }
+  kernel<<<2 * pairs, NUM_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, tout, static_cast<int>(a.M),
+                                                              static_cast<int>(a.N), static_cast<int>(a.K), group_m,
+                                                              ctx->status_dev);
   HB_CUDA_CHECK(cudaGetLastError());
   return HB200_OK;
 }
@@ -847,16 +882,9 @@ int launch_pair2_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& 
   const int64_t m_tiles = (a.M + PAIR2_BM - 1) / PAIR2_BM;
   const int64_t n_tiles = (a.N + PAIR2_BN - 1) / PAIR2_BN;
   const int pairs = static_cast<int>(std::min<int64_t>(m_tiles * n_tiles, ctx->num_sms / 2));
-  // output map: 32 x 32 element boxes, swizzled like the staging buffers the epilogue writes
   CUtensorMap tout;
   {
-    constexpr bool out32 = OUT_DT == HB200_DT_FP32;
-    const uint64_t elem = out32 ? 4 : 2;
-    const uint64_t dims[2] = {static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.M)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(a.ldc) * elem};
-    const uint32_t box[2] = {32, 32};
-    int rc = encode_tmap(&tout, out32 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, a.out, 2, dims,
-                         strides, box, out32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+    int rc = encode_out_map<OUT_DT>(&tout, a);
     if (rc != HB200_OK) return rc;
   }
   kernel<<<2 * pairs, PAIR2_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, tout, static_cast<int>(a.M),
@@ -972,30 +1000,38 @@ size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int 
   return splits > 1 ? static_cast<size_t>(splits) * M * N * sizeof(float) : 0;
 }
 
-// Chooses the table row with the smallest estimated time of the persistent schedule:
-//   waves x (outputs one SM produces per tile) / (measured tensor-pipe efficiency of the tile shape).
-// Efficiencies are the tensor-pipe-active fractions measured at 8192^3 on B200 (128x256: 0.75,
-// 128x128: 0.51, 128x64: 0.26, CTA pair 256x256: 0.78); a pair tile occupies two SMs.
+// Chooses the table row with the smallest estimated time of the persistent schedule, in SM cycles:
+//   waves x (K blocks x cycles per K block / measured tensor-pipe efficiency + exposed epilogue).
+// Efficiencies are tensor-pipe-active fractions measured at 8192^3 on B200: single-CTA 128x256 0.75,
+// 128x128 0.51, 128x64 0.26; CTA pair 256x256 (staged TMA-store epilogue, hidden behind the next
+// tile) 0.85; CTA pair 512x256 0.93 in the main loop but its epilogue (~4500 cycles) is exposed because
+// its two accumulators fill tensor memory -- so it wins for long K only.  A pair tile occupies two SMs.
 static int gemm_select_config_nosplit(int64_t M, int64_t N, int64_t K, bool y_colmajor, int num_sms) {
-  (void)K;
   struct Candidate {
     int cfg;
+    int64_t bm, bn;          // outputs per tile
+    bool pair;
+    double cycles_per_kb;    // at full tensor rate
     double eff;
+    double epilogue;         // exposed cycles per tile
   };
-  const Candidate candidates[4] = {{3, 0.75}, {1, 0.51}, {2, 0.26}, {7, 0.78}};
+  const Candidate candidates[5] = {
+      {3, 128, 256, false, 512.0, 0.75, 0.0},  {1, 128, 128, false, 256.0, 0.51, 0.0},
+      {2, 128, 64, false, 128.0, 0.26, 0.0},   {6, 256, 256, true, 512.0, 0.85, 0.0},
+      {14, 512, 256, true, 1024.0, 0.93, 4500.0},
+  };
+  const double k_blocks = static_cast<double>((K + BK - 1) / BK);
   int best = 3;
   double best_cost = -1.0;
-  for (const Candidate& cand : candidates) {
-    const GemmConfig& c = kGemmConfigs[cand.cfg];
-    if (!y_colmajor && !c.pair && c.bn < 128) continue;
-    const int64_t bm = c.pair ? PAIR_BM : BM;
+  for (const Candidate& c : candidates) {
+    if (!y_colmajor && c.bn < 128) continue;
     const int64_t slots = c.pair ? num_sms / 2 : num_sms;
-    const int64_t tiles = ((M + bm - 1) / bm) * ((N + c.bn - 1) / c.bn);
+    const int64_t tiles = ((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
     const int64_t waves = (tiles + slots - 1) / slots;
-    const double cost = static_cast<double>(waves) * 128.0 * c.bn / cand.eff;
+    const double cost = static_cast<double>(waves) * (k_blocks * c.cycles_per_kb / c.eff + c.epilogue);
     if (best_cost < 0 || cost < best_cost) {
       best_cost = cost;
-      best = cand.cfg;
+      best = c.cfg;
     }
   }
   return best;
@@ -1150,12 +1186,8 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
                         : launch_pair2_by_dtype<true>(a, ctx, ta, tb, c.group_m);
   }
   if (c.pair) {
-    if (c.stages == 6) {
-      return a.y_colmajor ? launch_pair_by_dtype<6, false>(a, ctx, ta, tb, c.group_m)
-                          : launch_pair_by_dtype<6, true>(a, ctx, ta, tb, c.group_m);
-    }
-    return a.y_colmajor ? launch_pair_by_dtype<7, false>(a, ctx, ta, tb, c.group_m)
-                        : launch_pair_by_dtype<7, true>(a, ctx, ta, tb, c.group_m);
+    return a.y_colmajor ? launch_pair_by_dtype<6, false>(a, ctx, ta, tb, c.group_m)
+                        : launch_pair_by_dtype<6, true>(a, ctx, ta, tb, c.group_m);
   }
   if (a.y_colmajor) {
     switch (c.bn) {
