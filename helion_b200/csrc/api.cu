@@ -4,6 +4,7 @@
 #include <cstring>
 #include <mutex>
 
+#include "common.cuh"
 #include "host.h"
 
 namespace hb {
@@ -142,6 +143,26 @@ int encode_tmap_u8(CUtensorMap* map, const void* base, int rank, const uint64_t*
 
 }  // namespace hb
 
+namespace hb {
+namespace selftest {
+// One CTA waits on an mbarrier that nothing arrives on; the bounded wait gives up after `limit_ns`,
+// records SITE_SELFTEST in the status word and the kernel returns normally.
+__global__ void wait_selftest_kernel(uint32_t* status, unsigned long long limit_ns, int* gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const WaitCtx wctx{&abort_flag, status};
+  const bool completed = mbar_wait_limited(&bar, 0, wctx, SITE_SELFTEST, limit_ns);
+  if (threadIdx.x == 0 && gave_up != nullptr) *gave_up = completed ? 0 : 1;
+}
+}  // namespace selftest
+}  // namespace hb
+
 using namespace hb;
 
 static int ctx_error_code(int device) {
@@ -176,6 +197,17 @@ int hb200_reset_status(int device) {
   DeviceCtx* ctx = get_device_ctx(device);
   if (ctx == nullptr) return HB200_ERR_CUDA;
   *reinterpret_cast<volatile uint32_t*>(ctx->status_host) = 0;
+  return HB200_OK;
+}
+
+int hb200_debug_wait_selftest(int device, int limit_ms, void* stream) {
+  if (limit_ms < 1 || limit_ms > 1000) return set_error(HB200_ERR_BAD_CONFIG, "wait self-test: limit must be 1..1000 ms");
+  DeviceCtx* ctx = get_device_ctx(device);
+  if (ctx == nullptr) return device_init_error(device);
+  DeviceGuard guard(device);
+  selftest::wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      ctx->status_dev, static_cast<unsigned long long>(limit_ms) * 1000000ull, nullptr);
+  HB_CUDA_CHECK(cudaGetLastError());
   return HB200_OK;
 }
 

@@ -45,6 +45,7 @@ enum WaitSite : uint32_t {
   SITE_ATTN_ALPHA = 21,
   SITE_ATTN_O_READY = 22,
   SITE_SPLITK = 30,
+  SITE_SELFTEST = 40,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -166,6 +167,24 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
     if (((++spins) & 0xffu) == 0u) {
       if (*ctx.abort_flag) return false;
       if (global_timer_ns() - t0 > HB_WAIT_LIMIT_NS) {
+        record_timeout(ctx, site);
+        return false;
+      }
+    }
+  }
+}
+
+// mbar_wait with an explicit limit (used by the wait self-test, which waits on a barrier that
+// nothing will ever complete in order to exercise the give-up path).
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, uint32_t site,
+                                                  unsigned long long limit_ns) {
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (((++spins) & 0xffu) == 0u) {
+      if (*ctx.abort_flag) return false;
+      if (global_timer_ns() - t0 > limit_ns) {
         record_timeout(ctx, site);
         return false;
       }

@@ -132,6 +132,13 @@ HB200_API int hb200_describe_config(int op, int cfg_id, char* buf, int buf_len);
 HB200_API int hb200_read_status(int device, uint32_t* site);
 HB200_API int hb200_reset_status(int device);
 
+/* Self-test of the bounded-wait scheme: launches one small CTA that waits on a barrier nothing will
+ * complete; after limit_ms (1..1000) the wait gives up, the kernel returns normally and the status
+ * word reports HB200_ERR_TIMEOUT with wait site 40.  The context stays usable.  (No counterpart in the
+ * reference: Helion's only timeout handling is around Triton compilation,
+ * helion/autotuner/base_search.py:155-200.) */
+HB200_API int hb200_debug_wait_selftest(int device, int limit_ms, void* stream);
+
 /* Number of SMs the persistent kernels size their grids with (cudaDevAttrMultiProcessorCount;
  * the role of helion/runtime/__init__.py:41-52 `get_num_sm`). */
 HB200_API int hb200_num_sms(int device);
