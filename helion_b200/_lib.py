@@ -27,6 +27,7 @@ ERR_WORKSPACE = -9
 DT_FP16, DT_BF16, DT_FP32, DT_E4M3 = 0, 1, 2, 3
 OP_GEMM, OP_ATTENTION = 0, 1
 STATIC_SCRATCH_BYTES = 4 << 20
+ATTN_WORKSPACE_BYTES = 16
 
 # Every symbol the header declares, with (restype, argtypes).
 _i64 = ctypes.c_int64
@@ -48,6 +49,11 @@ SIGNATURES = {
         ctypes.c_int,
         [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64x3, _i64x3, _i64x3, _i64x3, ctypes.c_float, ctypes.c_int,
          ctypes.c_int, ctypes.c_int, _vp],
+    ),
+    "hb200_fp8_attention_ws": (
+        ctypes.c_int,
+        [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64x3, _i64x3, _i64x3, _i64x3, ctypes.c_float, ctypes.c_int,
+         ctypes.c_int, _vp, ctypes.c_size_t, ctypes.c_int, _vp],
     ),
     "hb200_debug_wait_selftest": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _vp]),
     "hb200_num_configs": (ctypes.c_int, [ctypes.c_int]),

@@ -356,10 +356,13 @@ int hb200_fp8_gemm_splitk_static(const void* x, const void* y, void* out, int64_
   return launch_fp8_gemm_static_scratch(a, splits);
 }
 
-int hb200_fp8_attention(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S, int64_t D,
-                        const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
-                        const int64_t out_strides[3], float scale_log2, int out_dtype, int cfg_id, int device,
-                        void* stream) {
+// Validation and launch shared by the two attention entry points; workspace == nullptr selects
+// the static tile order.
+static int fp8_attention_impl(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S,
+                              int64_t D, const int64_t q_strides[3], const int64_t k_strides[3],
+                              const int64_t v_strides[3], const int64_t out_strides[3], float scale_log2,
+                              int out_dtype, int cfg_id, void* workspace, size_t workspace_bytes, int device,
+                              void* stream) {
   if (out_dtype != HB200_DT_E4M3 && out_dtype != HB200_DT_BF16 && out_dtype != HB200_DT_FP32) {
     return set_error(HB200_ERR_BAD_DTYPE, "fp8_attention: out_dtype must be E4M3, BF16 or FP32");
   }
@@ -415,8 +418,38 @@ int hb200_fp8_attention(const void* q, const void* k, const void* v, void* out, 
   a.cfg_id = cfg_id;
   a.device = device;
   a.stream = static_cast<cudaStream_t>(stream);
+  a.sched = nullptr;
   DeviceGuard guard(device);
+  if (workspace != nullptr) {
+    if (workspace_bytes < HB200_ATTN_WORKSPACE_BYTES) {
+      return set_error(HB200_ERR_WORKSPACE, "fp8_attention: workspace smaller than HB200_ATTN_WORKSPACE_BYTES");
+    }
+    if (reinterpret_cast<uintptr_t>(workspace) & 15u) {
+      return set_error(HB200_ERR_ALIGN, "fp8_attention: workspace must be 16-byte aligned");
+    }
+    // the tile counter starts at zero for every launch; the clear is ordered before the kernel on
+    // the same stream and allocates nothing
+    HB_CUDA_CHECK(cudaMemsetAsync(workspace, 0, HB200_ATTN_WORKSPACE_BYTES, a.stream));
+    a.sched = static_cast<unsigned int*>(workspace);
+  }
   return launch_fp8_attention(a, ctx);
+}
+
+int hb200_fp8_attention(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S, int64_t D,
+                        const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                        const int64_t out_strides[3], float scale_log2, int out_dtype, int cfg_id, int device,
+                        void* stream) {
+  return fp8_attention_impl(q, k, v, out, BH, S, D, q_strides, k_strides, v_strides, out_strides, scale_log2,
+                            out_dtype, cfg_id, nullptr, 0, device, stream);
+}
+
+int hb200_fp8_attention_ws(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S, int64_t D,
+                           const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                           const int64_t out_strides[3], float scale_log2, int out_dtype, int cfg_id, void* workspace,
+                           size_t workspace_bytes, int device, void* stream) {
+  if (workspace == nullptr) return set_error(HB200_ERR_WORKSPACE, "fp8_attention_ws: workspace is null");
+  return fp8_attention_impl(q, k, v, out, BH, S, D, q_strides, k_strides, v_strides, out_strides, scale_log2,
+                            out_dtype, cfg_id, workspace, workspace_bytes, device, stream);
 }
 
 }  // extern "C"

@@ -144,13 +144,18 @@ __device__ __forceinline__ void record_timeout(const WaitCtx& ctx, uint32_t site
 // aborting (this wait or another one ran out); the caller must then leave its loop.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, uint32_t site) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_timer_ns();
+  // The global timer is slow to read, so the clock of the limit only starts at the first check
+  // (256 failed polls in); a wait that is satisfied quickly never touches it.
+  unsigned long long t0 = 0ull;
   uint32_t spins = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if (((++spins) & 0xffu) == 0u) {
       if (*ctx.abort_flag) return false;
-      if (global_timer_ns() - t0 > HB_WAIT_LIMIT_NS) {
+      const unsigned long long now = global_timer_ns();
+      if (t0 == 0ull) {
+        t0 = now;
+      } else if (now - t0 > HB_WAIT_LIMIT_NS) {
         record_timeout(ctx, site);
         return false;
       }
@@ -160,13 +165,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
 
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, uint32_t site) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
-  const unsigned long long t0 = global_timer_ns();
+  // The global timer is slow to read, so the clock of the limit only starts at the first check
+  // (256 failed polls in); a wait that is satisfied quickly never touches it.
+  unsigned long long t0 = 0ull;
   uint32_t spins = 0;
   for (;;) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
     if (((++spins) & 0xffu) == 0u) {
       if (*ctx.abort_flag) return false;
-      if (global_timer_ns() - t0 > HB_WAIT_LIMIT_NS) {
+      const unsigned long long now = global_timer_ns();
+      if (t0 == 0ull) {
+        t0 = now;
+      } else if (now - t0 > HB_WAIT_LIMIT_NS) {
         record_timeout(ctx, site);
         return false;
       }
@@ -198,14 +208,17 @@ __device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity
 __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, uint32_t site,
                                                   uint32_t sleep_ns) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_timer_ns();
+  unsigned long long t0 = 0ull;  // set at the first check, see mbar_wait
   uint32_t spins = 0;
   for (;;) {
     __nanosleep(sleep_ns);
     if (mbar_try_wait(bar, parity)) return true;
     if (((++spins) & 0x3fu) == 0u) {
       if (*ctx.abort_flag) return false;
-      if (global_timer_ns() - t0 > HB_WAIT_LIMIT_NS) {
+      const unsigned long long now = global_timer_ns();
+      if (t0 == 0ull) {
+        t0 = now;
+      } else if (now - t0 > HB_WAIT_LIMIT_NS) {
         record_timeout(ctx, site);
         return false;
       }

@@ -6,7 +6,11 @@
 //   out = cast(acc / l)
 //
 // One CTA owns one (batch*head, 128-query-row) tile at a time and walks the keys in steps of 128;
-// CTAs are persistent, two per SM, so that one CTA's softmax overlaps the other's MMAs.
+// CTAs are persistent, two per SM, so that one CTA's softmax overlaps the other's MMAs.  The
+// producer hands out tiles: statically (blockIdx.x, + gridDim.x, ...) or, when the caller passes a
+// zeroed counter, from that counter, which evens out the different speeds of co-resident CTAs and
+// the last partial round.  Tile ids reach the other roles through a two-entry queue in shared
+// memory that rides on the Q barriers; -1 ends the kernel.
 //
 //   warp 0      TMA producer: Q tile, then K/V tiles through one ring of smem slots
 //   warp 1      MMA issuer (one thread): S = Q K^T into tensor memory, then O += P V with P read
@@ -31,37 +35,55 @@ namespace hb {
 namespace {
 
 constexpr int ATT_BM = 128;  // query rows per tile (= UMMA M, one row per softmax thread)
-constexpr int ATT_BN = 128;  // keys per step
+// keys per step: template parameter BN (128, or 64 for head_dim 64 where four CTAs fit one SM)
 constexpr int ATT_THREADS = 256;
 constexpr int ATT_SOFTMAX_THREADS = 128;
-constexpr int ATT_TMEM_COLS = 256;  // S: columns [0,128), O: columns [128, 128+D)
-constexpr int ATT_O_COL = 128;
+// tensor memory: S in columns [0, BN), O in columns [BN, BN + D); allocation = next power of two
 
-template <int D>
+template <int D, int BN>
 struct AttnLayout {
-  static constexpr int KV_STAGES = (D == 64) ? 8 : 4;
-  static constexpr int TILE_BYTES = 128 * D;  // one Q, K or V tile
+  static constexpr int CTAS_PER_SM = (D == 64 && BN == 64) ? 4 : 2;
+  static constexpr int TMEM_COLS = (BN + D <= 128) ? 128 : 256;
+  static constexpr int KV_STAGES = (BN == 64) ? 8 : ((D == 64) ? 8 : 4);
+  static constexpr int Q_BYTES = 128 * D;    // the Q tile
+  static constexpr int TILE_BYTES = BN * D;  // one K or V tile
   static constexpr int Q_OFFSET = 0;
-  static constexpr int P_OFFSET = TILE_BYTES;                 // 128 x 128 e4m3
-  static constexpr int KV_OFFSET = P_OFFSET + ATT_BM * ATT_BN;
+  static constexpr int P_OFFSET = Q_BYTES;                    // 128 x BN e4m3
+  static constexpr int KV_OFFSET = P_OFFSET + ATT_BM * BN;
   static constexpr int BAR_OFFSET = KV_OFFSET + KV_STAGES * TILE_BYTES;
   // q_full q_empty s_full s_free p_full pv_done drain kv_full[ST] kv_empty[ST]
   static constexpr int NUM_BARS = 7 + 2 * KV_STAGES;
   static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = MISC_OFFSET + 16 + 1024;
-  static_assert(SMEM_BYTES <= 113 * 1024, "two CTAs must fit one SM");
+  static_assert(SMEM_BYTES <= (CTAS_PER_SM == 4 ? 56 : 113) * 1024, "the CTAs must fit one SM together");
 };
 
-__device__ __forceinline__ void reg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
-__device__ __forceinline__ void reg_inc_200() { asm volatile("setmaxnreg.inc.sync.aligned.u32 200;"); }
+// two CTAs per SM: 256 threads x 128 registers at launch -> 128 x 56 + 128 x 200
+// four CTAs per SM: 256 threads x 64 registers at launch -> 128 x 24 + 128 x 104
+template <int CTAS>
+__device__ __forceinline__ void reg_dec_wg0() {
+  if constexpr (CTAS == 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
+  else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+}
+template <int CTAS>
+__device__ __forceinline__ void reg_inc_softmax() {
+  if constexpr (CTAS == 4) asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+  else asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+}
 
-template <int D, bool V_KMAJOR, int OUT_DT, int POLY_OF8, bool LAZY>
-__global__ void __launch_bounds__(ATT_THREADS, 2)
+template <int D, int BN, bool V_KMAJOR, int OUT_DT, int POLY_OF8, bool LAZY>
+__global__ void __launch_bounds__(ATT_THREADS, (D == 64 && BN == 64) ? 4 : 2)
 fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, void* out, int BH, int S, int64_t out_stride_bh,
-                     int64_t out_stride_s, float scale_log2, uint32_t* status) {
-  using L = AttnLayout<D>;
+                     int64_t out_stride_s, float scale_log2, uint32_t* status, unsigned int* sched) {
+  using L = AttnLayout<D, BN>;
   constexpr int ST = L::KV_STAGES;
+  constexpr int ATT_BN = BN;
+  constexpr int ATT_O_COL = BN;
+  constexpr int ATT_TMEM_COLS = L::TMEM_COLS;
+  // P rows are BN bytes long: 128-byte or 64-byte swizzle, 8-row atoms
+  constexpr uint32_t SWZ_P = (BN == 128) ? SWZ_128B : SWZ_64B;
+  constexpr uint32_t SBO_P = 8 * BN;
   constexpr uint32_t SWZ_QK = (D == 128) ? SWZ_128B : SWZ_64B;  // rows of Q/K/V tiles are D bytes long
   constexpr uint32_t SBO_QK = 8 * D;
 
@@ -79,6 +101,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint64_t* kv_empty = bars + 7 + ST;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFFSET + 4);
+  volatile int* tile_q = reinterpret_cast<volatile int*>(smem + L::MISC_OFFSET + 8);  // [2], indexed by tile parity
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -89,7 +112,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
+    mbar_init(q_empty, 1 + ATT_SOFTMAX_THREADS);  // last Q K^T of the tile + every softmax thread has the tile id
     mbar_init(s_full, 1);
     mbar_init(s_free, ATT_SOFTMAX_THREADS);
     mbar_init(p_full, ATT_SOFTMAX_THREADS);
@@ -113,7 +136,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4) {
-    reg_dec_56();
+    reg_dec_wg0<L::CTAS_PER_SM>();
     if (warp == 0) {
       // ------------------------------- TMA producer ------------------------------------------
       if (lane == 0) {
@@ -123,15 +146,25 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         uint32_t slot_it = 0;  // running K/V tile counter (ring position)
         uint32_t tile_iter = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
-          const int bh = tile / m_tiles;
-          const int mt = tile - bh * m_tiles;
+        int tile = blockIdx.x;  // gridDim.x <= num_tiles
+        for (;; ++tile_iter) {
+          // Q buffer and queue entry of this parity are free once the tile two back is done with them
           if (!mbar_wait_relaxed(q_empty, (tile_iter & 1u) ^ 1u, wctx, SITE_ATTN_Q, 200)) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(q_full, L::TILE_BYTES);
+          tile_q[tile_iter & 1u] = tile;
+          if (tile < 0) {
+            mbar_arrive(q_full);  // publishes the end marker
+            break;
+          }
+          const int bh = tile / m_tiles;
+          const int mt = tile - bh * m_tiles;
+          mbar_arrive_expect_tx(q_full, L::Q_BYTES);
           tma_load_3d(smem + L::Q_OFFSET, &tmap_q, q_full, 0, mt * ATT_BM, bh);
+          // the next tile: asked for now, needed after this tile's loads are issued
+          int next = sched != nullptr ? static_cast<int>(gridDim.x + atomicAdd(sched, 1u)) : tile + static_cast<int>(gridDim.x);
+          if (next >= num_tiles || next < 0) next = -1;
           for (int j = 0; j < n_steps && ok; ++j) {
 #pragma unroll
             for (int kv = 0; kv < 2; ++kv, ++slot_it) {
@@ -152,6 +185,8 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
               }
             }
           }
+          if (!ok) break;
+          tile = next;
         }
         if (!ok) {
           mbar_drain(q_full, tile_iter & 1u);
@@ -171,7 +206,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const uint32_t t_s = tmem_base;
         const uint32_t t_o = tmem_base + ATT_O_COL;
         const uint64_t q_desc = make_smem_desc(q_addr, 16, SBO_QK, SWZ_QK);
-        const uint64_t p_desc = make_smem_desc(p_addr, 16, 1024, SWZ_128B);
+        const uint64_t p_desc = make_smem_desc(p_addr, 16, SBO_P, SWZ_P);
         uint32_t g = 0;        // running step counter: phases of s_full / s_free / p_full / pv_done
         uint32_t slot_it = 0;  // ring position of the K tile of the step whose Q K^T is issued next
         uint32_t tile_iter = 0;
@@ -194,11 +229,12 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           return true;
         };
 
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
+        for (; ok; ++tile_iter) {
           if (!mbar_wait_relaxed(q_full, tile_iter & 1u, wctx, SITE_ATTN_Q, 100)) {
             ok = false;
             break;
           }
+          if (tile_q[tile_iter & 1u] < 0) break;  // no more tiles
           if (!issue_qk(slot_it, g, n_steps == 1)) {
             ok = false;
             break;
@@ -221,7 +257,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             const uint32_t v_addr = kv_addr + vs * L::TILE_BYTES;
             // V [keys, D] with D contiguous: MN-major B, one swizzle-wide block of N, 8 key rows per
             // atom.  V [D, keys] with keys contiguous: K-major B with 128-byte rows.
-            const uint64_t v_desc = V_KMAJOR ? make_smem_desc(v_addr, 16, 1024, SWZ_128B)
+            const uint64_t v_desc = V_KMAJOR ? make_smem_desc(v_addr, 16, SBO_P, SWZ_P)
                                              : make_smem_desc(v_addr, SBO_QK, SBO_QK, SWZ_QK);
 #pragma unroll
             for (int k = 0; k < ATT_BN / 32; ++k) {
@@ -242,19 +278,26 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     }
   } else {
     // --------------------------------- softmax / epilogue --------------------------------------
-    reg_inc_200();
+    reg_inc_softmax<L::CTAS_PER_SM>();
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t t_s = tmem_base + lane_sel;
     const uint32_t t_o = tmem_base + ATT_O_COL + lane_sel;
-    // P tile, 128-byte rows, 16-byte chunks XOR-swizzled with (row % 8)
-    uint8_t* p_row = smem + L::P_OFFSET + (row_in_tile >> 3) * 1024 + (row_in_tile & 7) * 128;
-    const uint32_t p_xor = static_cast<uint32_t>(row_in_tile & 7);
+    // P tile: BN-byte rows, 16-byte chunks XOR-swizzled with (row % 8) for 128-byte rows or with
+    // ((row >> 1) % 4) for 64-byte rows
+    uint8_t* p_row = smem + L::P_OFFSET + row_in_tile * BN;
+    const uint32_t p_xor = (BN == 128) ? static_cast<uint32_t>(row_in_tile & 7) : static_cast<uint32_t>((row_in_tile >> 1) & 3);
     uint32_t g = 0;
     bool ok = true;
 
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (uint32_t tile_iter = 0; ok; ++tile_iter) {
+      ok = mbar_wait(q_full, tile_iter & 1u, wctx, SITE_ATTN_Q);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int tile = tile_q[tile_iter & 1u];
+      mbar_arrive(q_empty);  // this thread has the id; the entry may be reused two tiles on
+      if (tile < 0) break;
       const int bh = tile / m_tiles;
       const int mt = tile - bh * m_tiles;
       float m_i = -INFINITY;
@@ -264,9 +307,10 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        uint32_t s[4][32];
+        constexpr int NC = BN / 32;  // 32-column chunks of the score row
+        uint32_t s[NC][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, s[c]);
+        for (int c = 0; c < NC; ++c) tmem_ld_32x32b_x32(t_s + c * 32, s[c]);
         tmem_wait_ld();
         tc_fence_before_sync();
         mbar_arrive(s_free);  // S may be overwritten by the next Q K^T
@@ -274,7 +318,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const int valid = S - j * ATT_BN;  // keys of this step that exist
         if (valid < ATT_BN) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < NC; ++c) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               if (c * 32 + i >= valid) s[c][i] = __float_as_uint(-INFINITY);
@@ -284,7 +328,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         // row max: 3-input max, four independent chains
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < NC; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             mx0 = fmax3(mx0, __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
@@ -308,9 +352,9 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const uint64_t c2 = pack2f(scale_log2, scale_log2);
         const uint64_t negm2 = pack2f(-m_new, -m_new);
         uint64_t sum_a = 0ull, sum_b = 0ull;  // two (0.0f, 0.0f) pairs
-        uint32_t packed[32];
+        uint32_t packed[BN / 4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < NC; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             const int pair0 = (c * 32 + i) / 2;
@@ -355,7 +399,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           }
         }
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
+        for (int ch = 0; ch < BN / 16; ++ch) {
           *reinterpret_cast<uint4*>(p_row + ((static_cast<uint32_t>(ch) ^ p_xor) << 4)) =
               make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
         }
@@ -433,22 +477,31 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 struct AttnConfig {
   int poly_of8;  // of every 8 pairs of exponentials, how many use the FMA-pipe polynomial
   bool lazy;     // rescale O only when a row max grew by more than 2^8
+  int bn;        // keys per step; 64 exists for head_dim 64 only (head_dim 128 then runs 128-key steps)
   const char* note;
 };
 const AttnConfig kAttnConfigs[] = {
-    {0, false, "exact running max (rescale whenever a row max moves), all exp2 on the MUFU unit"},
-    {0, true, "lazy rescale (only when a row max grew by more than 2^8), all exp2 on the MUFU unit"},
-    {2, true, "lazy rescale, 2 of 8 exp2 pairs on the FMA pipes (degree-3 polynomial)"},
-    {4, true, "lazy rescale, 4 of 8 exp2 pairs on the FMA pipes"},
+    {0, false, 128, "exact running max (rescale whenever a row max moves), all exp2 on the MUFU unit"},
+    {0, true, 128, "lazy rescale (only when a row max grew by more than 2^8), all exp2 on the MUFU unit"},
+    {2, true, 128, "lazy rescale, 2 of 8 exp2 pairs on the FMA pipes (degree-3 polynomial)"},
+    {4, true, 128, "lazy rescale, 4 of 8 exp2 pairs on the FMA pipes"},
+    {0, false, 64, "exact running max, 64-key steps with four CTAs per SM for head_dim 64 (128-key steps otherwise)"},
+    {0, true, 64, "lazy rescale, 64-key steps with four CTAs per SM for head_dim 64 (128-key steps otherwise)"},
 };
-constexpr int kNumAttnConfigs = 4;
+constexpr int kNumAttnConfigs = 6;
 constexpr int kDefaultAttnConfig = 0;
 
-template <int D, bool V_KMAJOR, int OUT_DT, int POLY_OF8, bool LAZY>
+// keys per step that a table row means for a head dimension
+int attn_block_n(int cfg_id, int64_t d) {
+  const int cfg = cfg_id < 0 ? kDefaultAttnConfig : cfg_id;
+  return (kAttnConfigs[cfg].bn == 64 && d == 64) ? 64 : 128;
+}
+
+template <int D, int BN, bool V_KMAJOR, int OUT_DT, int POLY_OF8, bool LAZY>
 int launch_attn_poly(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, const CUtensorMap& tk,
                      const CUtensorMap& tv) {
-  using L = AttnLayout<D>;
-  auto kernel = fp8_attention_kernel<D, V_KMAJOR, OUT_DT, POLY_OF8, LAZY>;
+  using L = AttnLayout<D, BN>;
+  auto kernel = fp8_attention_kernel<D, BN, V_KMAJOR, OUT_DT, POLY_OF8, LAZY>;
   static bool attr_set[64] = {};
   if (!attr_set[a.device]) {
     HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
@@ -457,10 +510,10 @@ int launch_attn_poly(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, c
   const int64_t m_tiles = (a.S + ATT_BM - 1) / ATT_BM;
   const int64_t num_tiles = a.BH * m_tiles;
   if (num_tiles > INT32_MAX) return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: too many tiles");
-  const int grid = static_cast<int>(std::min<int64_t>(num_tiles, 2 * ctx->num_sms));
+  const int grid = static_cast<int>(std::min<int64_t>(num_tiles, L::CTAS_PER_SM * ctx->num_sms));
   kernel<<<grid, ATT_THREADS, L::SMEM_BYTES, a.stream>>>(tq, tk, tv, a.out, static_cast<int>(a.BH),
                                                          static_cast<int>(a.S), a.out_strides[0], a.out_strides[1],
-                                                         a.scale_log2, ctx->status_dev);
+                                                         a.scale_log2, ctx->status_dev, a.sched);
   HB_CUDA_CHECK(cudaGetLastError());
   return HB200_OK;
 }
@@ -470,14 +523,20 @@ int launch_attn_instance(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& t
                          const CUtensorMap& tv) {
   const int cfg = a.cfg_id < 0 ? kDefaultAttnConfig : a.cfg_id;
   const AttnConfig& c = kAttnConfigs[cfg];
-  if (!c.lazy) return launch_attn_poly<D, V_KMAJOR, OUT_DT, 0, false>(a, ctx, tq, tk, tv);
+  if constexpr (D == 64) {
+    if (c.bn == 64) {
+      return c.lazy ? launch_attn_poly<D, 64, V_KMAJOR, OUT_DT, 0, true>(a, ctx, tq, tk, tv)
+                    : launch_attn_poly<D, 64, V_KMAJOR, OUT_DT, 0, false>(a, ctx, tq, tk, tv);
+    }
+  }
+  if (!c.lazy) return launch_attn_poly<D, 128, V_KMAJOR, OUT_DT, 0, false>(a, ctx, tq, tk, tv);
   switch (c.poly_of8) {
     case 0:
-      return launch_attn_poly<D, V_KMAJOR, OUT_DT, 0, true>(a, ctx, tq, tk, tv);
+      return launch_attn_poly<D, 128, V_KMAJOR, OUT_DT, 0, true>(a, ctx, tq, tk, tv);
     case 2:
-      return launch_attn_poly<D, V_KMAJOR, OUT_DT, 2, true>(a, ctx, tq, tk, tv);
+      return launch_attn_poly<D, 128, V_KMAJOR, OUT_DT, 2, true>(a, ctx, tq, tk, tv);
     case 4:
-      return launch_attn_poly<D, V_KMAJOR, OUT_DT, 4, true>(a, ctx, tq, tk, tv);
+      return launch_attn_poly<D, 128, V_KMAJOR, OUT_DT, 4, true>(a, ctx, tq, tk, tv);
     default:
       return set_error(HB200_ERR_BAD_CONFIG, "fp8_attention: config has no kernel instance");
   }
@@ -512,27 +571,30 @@ int launch_fp8_attention(const AttnArgs& a, DeviceCtx* ctx) {
   const bool v_kmajor = a.v_strides[2] == 1 && a.v_strides[1] != 1;  // keys contiguous
   const uint32_t d = static_cast<uint32_t>(a.D);
   const CUtensorMapSwizzle swz_d = a.D == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  const uint32_t bn = static_cast<uint32_t>(attn_block_n(a.cfg_id, a.D));
   CUtensorMap tq, tk, tv;
   int rc;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(a.D), static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.BH)};
     const uint32_t box[3] = {d, 128, 1};
+    const uint32_t kvbox[3] = {d, bn, 1};
     const uint64_t qs[2] = {static_cast<uint64_t>(a.q_strides[1]), static_cast<uint64_t>(a.q_strides[0])};
     rc = encode_tmap_u8(&tq, a.q, 3, dims, qs, box, swz_d);
     if (rc != HB200_OK) return rc;
     const uint64_t ks[2] = {static_cast<uint64_t>(a.k_strides[1]), static_cast<uint64_t>(a.k_strides[0])};
-    rc = encode_tmap_u8(&tk, a.k, 3, dims, ks, box, swz_d);
+    rc = encode_tmap_u8(&tk, a.k, 3, dims, ks, kvbox, swz_d);
     if (rc != HB200_OK) return rc;
     if (!v_kmajor) {
       // physical [BH, S, D]: logical strides {bh, d, s} = {v_strides[0], 1, v_strides[2]}
       const uint64_t vs[2] = {static_cast<uint64_t>(a.v_strides[2]), static_cast<uint64_t>(a.v_strides[0])};
-      rc = encode_tmap_u8(&tv, a.v, 3, dims, vs, box, swz_d);
+      rc = encode_tmap_u8(&tv, a.v, 3, dims, vs, kvbox, swz_d);
       if (rc != HB200_OK) return rc;
     } else {
       const uint64_t vdims[3] = {static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.D), static_cast<uint64_t>(a.BH)};
-      const uint32_t vbox[3] = {128, d, 1};
+      const uint32_t vbox[3] = {bn, d, 1};
       const uint64_t vs[2] = {static_cast<uint64_t>(a.v_strides[1]), static_cast<uint64_t>(a.v_strides[0])};
-      rc = encode_tmap_u8(&tv, a.v, 3, vdims, vs, vbox, CU_TENSOR_MAP_SWIZZLE_128B);
+      rc = encode_tmap_u8(&tv, a.v, 3, vdims, vs, vbox,
+                          bn == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
       if (rc != HB200_OK) return rc;
     }
   }

@@ -106,6 +106,7 @@ struct AttnArgs {
   int cfg_id;
   int device;
   cudaStream_t stream;
+  unsigned int* sched;  // zeroed tile counter in device memory, or null for the static tile order
 };
 
 int launch_fp8_attention(const AttnArgs& args, DeviceCtx* ctx);

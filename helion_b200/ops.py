@@ -103,14 +103,15 @@ def fp8_attention(
     out_dtype: torch.dtype = torch.float8_e4m3fn,
     config: Optional[int] = None,
     out: Optional[torch.Tensor] = None,
+    balanced: Optional[bool] = None,
 ) -> torch.Tensor:
     """Non-causal FP8 attention forward with the reference's numerics.
 
     Same contract as the reference's ``fp8_attention_kernel(q, k, v, batch, heads)``
     (examples/fp8_attention.py:22-106): ``q``, ``k`` are ``[batch*heads, seq, dim]`` e4m3, ``v`` is
     the "pre-transposed" ``[batch*heads, dim, seq]`` e4m3 tensor (either physical layout), the
-    result is ``[batch, heads, seq, dim]`` e4m3.  ``out_dtype`` (e4m3 / bf16 / fp32), ``config`` and
-    ``out`` are keyword-only extensions.
+    result is ``[batch, heads, seq, dim]`` e4m3.  ``out_dtype`` (e4m3 / bf16 / fp32), ``config``,
+    ``out`` and ``balanced`` (see :func:`attention_into`) are keyword-only extensions.
     """
     for name, t in (("q", q), ("k", k), ("v", v)):
         if t.dtype != torch.float8_e4m3fn:
@@ -140,17 +141,25 @@ def fp8_attention(
         raise ValueError("fp8_attention: `out` must be a contiguous [batch, heads, seq, dim] tensor of out_dtype")
     if bh == 0 or s == 0:
         return out
-    attention_into(q, k, v, out.view(bh, s, d), config=config)
+    attention_into(q, k, v, out.view(bh, s, d), config=config, balanced=balanced)
     return out
 
 
 def attention_into(
-    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out3: torch.Tensor, *, config: Optional[int] = None
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out3: torch.Tensor, *, config: Optional[int] = None,
+    balanced: Optional[bool] = None,
 ) -> None:
     """Launch the attention kernel on ``[BH,S,D]`` / ``[BH,D,S]`` tensors, writing ``out3 [BH,S,D]``.
 
     The batch*head slices are independent, so a shard of them (a slice along dim 0 of every
     tensor) is a valid call; the multi-GPU driver uses exactly that.
+
+    ``balanced=True`` lets the CTAs draw tiles from a counter in a 16-byte workspace that this
+    wrapper takes from torch's caching allocator per call (stream-ordered, so overlapping calls on
+    other streams never share it); ``balanced=False`` is the fixed round-robin of
+    ``hb200_fp8_attention``.  Results are bit-identical either way.  The default (``None``) uses the
+    counter from 2048 keys up: measured on B200 it shortens the kernel by 4-10 % at seq 4096 and
+    gains nothing at seq 1024, where clearing the counter costs what the better balance saves.
     """
     bh, s, d = q.shape
     dev = _require_cuda(q, k, v, out3)
@@ -158,9 +167,20 @@ def attention_into(
     scale_log2 = (1.0 / math.sqrt(float(d))) * 1.44269504
     arr = ctypes.c_int64 * 3
     lib = _lib.load()
-    code = lib.hb200_fp8_attention(
-        q.data_ptr(), k.data_ptr(), v.data_ptr(), out3.data_ptr(), bh, s, d,
-        arr(*q.stride()), arr(*k.stride()), arr(*v.stride()), arr(*out3.stride()),
-        scale_log2, _OUT_DT[out3.dtype], -1 if config is None else int(config), dev, _stream_ptr(dev),
-    )
+    cfg = -1 if config is None else int(config)
+    if balanced is None:
+        balanced = s >= 2048
+    if balanced:
+        ws = torch.empty(_lib.ATTN_WORKSPACE_BYTES, dtype=torch.uint8, device=q.device)
+        code = lib.hb200_fp8_attention_ws(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out3.data_ptr(), bh, s, d,
+            arr(*q.stride()), arr(*k.stride()), arr(*v.stride()), arr(*out3.stride()),
+            scale_log2, _OUT_DT[out3.dtype], cfg, ws.data_ptr(), ws.numel(), dev, _stream_ptr(dev),
+        )
+    else:
+        code = lib.hb200_fp8_attention(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out3.data_ptr(), bh, s, d,
+            arr(*q.stride()), arr(*k.stride()), arr(*v.stride()), arr(*out3.stride()),
+            scale_log2, _OUT_DT[out3.dtype], cfg, dev, _stream_ptr(dev),
+        )
     _lib.raise_for(code, "fp8_attention")

@@ -96,6 +96,26 @@ HB200_API int hb200_fp8_attention(const void* q, const void* k, const void* v, v
                         const int64_t out_strides[3], float scale_log2, int out_dtype, int cfg_id, int device,
                         void* stream);
 
+/* hb200_fp8_attention with a balanced tile order.  Same computation, arguments and results
+ * (bit-identical: each output tile is computed by the same code whichever CTA takes it); the only
+ * difference is which CTA computes which 128-row tile.  hb200_fp8_attention hands tiles out in a
+ * fixed round-robin, so the kernel ends when the slowest CTA has finished its share; co-resident
+ * CTAs run at different speeds and the last round is usually partial.  Here the CTAs draw tiles
+ * from a counter in `workspace`, which shortens the kernel by roughly a tenth.  The Helion kernel
+ * it replaces is examples/fp8_attention.py:22-106, as for hb200_fp8_attention; the reference has no
+ * workspace argument (its grid is one program per batch*head, fp8_attention.py:54).
+ *   workspace: HB200_ATTN_WORKSPACE_BYTES of device memory, 16-byte aligned, owned by the caller.
+ *      The call clears it on `stream` before the kernel (no allocation); it must not be shared by
+ *      calls that can overlap in time (other streams), and may be reused by the next call on the
+ *      same stream.
+ */
+#define HB200_ATTN_WORKSPACE_BYTES 16u
+HB200_API int hb200_fp8_attention_ws(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S,
+                           int64_t D, const int64_t q_strides[3], const int64_t k_strides[3],
+                           const int64_t v_strides[3], const int64_t out_strides[3], float scale_log2,
+                           int out_dtype, int cfg_id, void* workspace, size_t workspace_bytes, int device,
+                           void* stream);
+
 /* Split-K FP8 GEMM that allocates nothing: same computation and arguments as hb200_fp8_gemm with a
  * split-K row of the table, but the fp32 partial sums live in a fixed array compiled into the
  * library instead of a caller-provided workspace.  It has no counterpart in the reference; it
