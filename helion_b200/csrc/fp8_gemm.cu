@@ -809,6 +809,7 @@ struct GemmConfig {
   bool pair;     // CTA-pair kernel (256 x 256 tiles) instead of the single-CTA kernel (128 x bn)
   int splits;    // split-K factor (needs a workspace of splits x M x N floats when > 1)
   const char* note;
+  bool skinny = false;  // operand-swapped kernel for M <= 64, column-major y (fp8_gemm_skinny.cu)
 };
 
 const GemmConfig kGemmConfigs[] = {
@@ -830,6 +831,9 @@ const GemmConfig kGemmConfigs[] = {
     {512, 4, 4, true, 1, "CTA pair, 512x256x128 tiles (256x256 per CTA, two accumulators), 4 stages, group_m 4"},
     {512, 4, 2, true, 1, "CTA pair, 512x256x128 tiles (256x256 per CTA, two accumulators), 4 stages, group_m 2"},
     {512, 4, 16, true, 1, "CTA pair, 512x256x128 tiles (256x256 per CTA, two accumulators), 4 stages, group_m 16"},
+    {128, 12, 1, false, 1, "M <= 64, column-major y: operands swapped (128 columns of y x 16/32/64 rows of x), 9-12 stages", true},
+    {128, 12, 1, false, 2, "M <= 64, column-major y: operands swapped, split-K 2", true},
+    {128, 12, 1, false, 4, "M <= 64, column-major y: operands swapped, split-K 4", true},
 };
 constexpr int kNumGemmConfigs = sizeof(kGemmConfigs) / sizeof(kGemmConfigs[0]);
 
@@ -956,14 +960,7 @@ int launch_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, co
                                                          static_cast<int>(a.K), a.ldc, group_m, ctx->status_dev, splits,
                                                          static_cast<float*>(a.workspace));
   HB_CUDA_CHECK(cudaGetLastError());
-  if (splits > 1) {
-    const int64_t threads_total = a.M * (a.N / 8);
-    const int blocks = static_cast<int>((threads_total + 255) / 256);
-    splitk_reduce_kernel<OUT_DT><<<blocks, 256, 0, a.stream>>>(static_cast<const float*>(a.workspace), a.out,
-                                                              static_cast<int>(a.M), static_cast<int>(a.N), a.ldc, splits);
-    HB_CUDA_CHECK(cudaGetLastError());
-  }
-  return HB200_OK;
+  return splits > 1 ? launch_splitk_reduce(a, splits) : HB200_OK;
 }
 
 template <int BN, int STAGES, bool B_MN>
@@ -983,11 +980,34 @@ int launch_by_dtype(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, co
 
 }  // namespace
 
+int launch_splitk_reduce(const GemmArgs& a, int splits) {
+  const int64_t threads_total = a.M * (a.N / 8);
+  const int blocks = static_cast<int>((threads_total + 255) / 256);
+  const float* partials = static_cast<const float*>(a.workspace);
+  const int m = static_cast<int>(a.M), n = static_cast<int>(a.N);
+  switch (a.out_dtype) {
+    case HB200_DT_FP16:
+      splitk_reduce_kernel<HB200_DT_FP16><<<blocks, 256, 0, a.stream>>>(partials, a.out, m, n, a.ldc, splits);
+      break;
+    case HB200_DT_BF16:
+      splitk_reduce_kernel<HB200_DT_BF16><<<blocks, 256, 0, a.stream>>>(partials, a.out, m, n, a.ldc, splits);
+      break;
+    case HB200_DT_FP32:
+      splitk_reduce_kernel<HB200_DT_FP32><<<blocks, 256, 0, a.stream>>>(partials, a.out, m, n, a.ldc, splits);
+      break;
+    default:
+      return set_error(HB200_ERR_BAD_DTYPE, "fp8_gemm: unsupported out_dtype");
+  }
+  HB_CUDA_CHECK(cudaGetLastError());
+  return HB200_OK;
+}
+
 int gemm_num_configs() { return kNumGemmConfigs; }
 
 int gemm_describe_config(int cfg_id, char* buf, int buf_len) {
   if (cfg_id < 0 || cfg_id >= kNumGemmConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: no such config");
   const GemmConfig& c = kGemmConfigs[cfg_id];
+  if (c.skinny) return std::snprintf(buf, buf_len, "gemm cfg %d: split_k=%d (%s)", cfg_id, c.splits, c.note);
   return std::snprintf(buf, buf_len, "gemm cfg %d: BM=%d BN=%d BK=128 stages=%d group_m=%d split_k=%d (%s)", cfg_id,
                        c.bn == 512 ? 512 : (c.pair ? 256 : 128), c.bn == 512 ? 256 : c.bn, c.stages, c.group_m, c.splits,
                        c.note);
@@ -1055,8 +1075,24 @@ static int select_splitk_config(int64_t M, int64_t N, int64_t K, int num_sms) {
   return splits == 2 ? 11 : (splits == 4 ? 12 : 13);
 }
 
+// Rows of the operand-swapped kernel.  Measured on B200, cold L2, bf16 out, K = 4096, N = 14336:
+// M = 16: 21.5 us against 25.6 us for the 128x128 row (cuBLASLt 19.5 us); from M = 33 up (64 rows of x
+// per stage, 9 stages) the general row is as fast or faster, so the automatic choice stops at 32.
+// Split-K pays only when the column blocks alone leave most SMs idle (N = 4096, K = 14336: 25.6 us with
+// 4 splits against 41.1 us without); with 112 column blocks its second kernel costs more than it gains.
+static int select_skinny_config(int64_t M, int64_t N, int64_t K, bool y_colmajor, int num_sms) {
+  if (!gemm_skinny_supported(M, y_colmajor) || M > 32) return -1;
+  const int64_t n_tiles = (N + 127) / 128;
+  const int64_t k_blocks = (K + BK - 1) / BK;
+  if (n_tiles * 4 <= num_sms && k_blocks >= 32) return 20;
+  if (n_tiles * 2 <= num_sms && k_blocks >= 16) return 19;
+  return 18;
+}
+
 int gemm_select_config(int64_t M, int64_t N, int64_t K, bool y_colmajor, int out_dtype, int num_sms) {
   (void)out_dtype;
+  const int skinny_cfg = select_skinny_config(M, N, K, y_colmajor, num_sms);
+  if (skinny_cfg >= 0) return skinny_cfg;
   const int split_cfg = select_splitk_config(M, N, K, num_sms);
   if (split_cfg >= 0) return split_cfg;
   return gemm_select_config_nosplit(M, N, K, y_colmajor, num_sms);
@@ -1150,11 +1186,12 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
     // The table's split-K rows need scratch; a caller that passed none gets the best row without.
     if (kGemmConfigs[cfg_id].splits > 1 &&
         (a.workspace == nullptr || a.workspace_bytes < gemm_workspace_bytes(a.M, a.N, a.K, a.out_dtype, cfg_id))) {
-      cfg_id = gemm_select_config_nosplit(a.M, a.N, a.K, a.y_colmajor, ctx->num_sms);
+      cfg_id = kGemmConfigs[cfg_id].skinny ? 18 : gemm_select_config_nosplit(a.M, a.N, a.K, a.y_colmajor, ctx->num_sms);
     }
   }
   if (cfg_id >= kNumGemmConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: no such config");
   const GemmConfig& c = kGemmConfigs[cfg_id];
+  if (c.skinny) return launch_fp8_gemm_skinny(a, ctx, effective_splits(a.K, c.splits));
   if (!a.y_colmajor && c.bn < 128) {
     return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: this config supports column-major y only");
   }

@@ -86,6 +86,13 @@ int gemm_describe_config(int cfg_id, char* buf, int buf_len);
 int gemm_select_config(int64_t M, int64_t N, int64_t K, bool y_colmajor, int out_dtype, int num_sms);
 size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int cfg_id);
 
+// The operand-swapped kernel for M <= 64 and column-major y (fp8_gemm_skinny.cu); splits > 1 writes
+// fp32 partial sums to args.workspace and runs the ordered reduction.
+bool gemm_skinny_supported(int64_t M, bool y_colmajor);
+int launch_fp8_gemm_skinny(const GemmArgs& args, DeviceCtx* ctx, int splits);
+// out = cast(sum over splits of workspace[split][M][N]), in split order.
+int launch_splitk_reduce(const GemmArgs& args, int splits);
+
 // Split-K launch whose partial sums live in the library's static device array (no allocation).
 int launch_fp8_gemm_static_scratch(const GemmArgs& args, int splits);
 // Makes the tensor-map encoder available without creating a device context (no allocation).

@@ -90,6 +90,11 @@ def test_every_table_config_gives_the_same_result(hb):
     x, y = o.gemm_inputs(520, 784, 1152, seed=5)
     base = None
     for cfg in range(_lib.num_configs(_lib.OP_GEMM)):
+        if "M <= 64" in _lib.describe_config(_lib.OP_GEMM, cfg):
+            # the operand-swapped rows are for few rows of x: they must refuse this problem
+            with pytest.raises(ValueError, match="M <= 64"):
+                hb.fp8_gemm(to_dev(x), to_dev(y), config=cfg)
+            continue
         got, _ = check_against_oracle(hb, x, y, torch.float32, config=cfg)
         base = got if base is None else base
         np.testing.assert_allclose(got, base, rtol=1e-5, atol=1e-4)
@@ -112,6 +117,37 @@ def test_split_k_configs_match_oracle(hb, m, n, k, colmajor):
         for dt in (torch.float32, torch.bfloat16, torch.float16):
             got, _ = check_against_oracle(hb, x, y, dt, config=cfg)
         np.testing.assert_allclose(got, o.round_to_dtype(base, "fp16"), rtol=2e-3, atol=2e-2)
+
+
+@pytest.mark.parametrize(
+    "m,n,k",
+    [(16, 14336, 4096), (33, 14336, 4096), (16, 4096, 14336)]  # the MLP shape, a longer K that splits
+    + [(m, 2000, 528) for m in (1, 7, 16, 17, 32, 33, 64)]       # every row count class, ragged N and K
+    + [(1, 136, 16), (64, 136, 16)],                             # one K block of 16
+)
+def test_few_rows_of_x_use_the_operand_swapped_kernel(hb, m, n, k):
+    """M <= 64 against a column-major y (the decode-time MLP shape): rows 18-20 of the table compute
+    out^T with the columns of y as the UMMA rows.  Same products, same fp32 accumulation order along
+    K, so the unsplit row must equal the general 128x128 row bit for bit in every output dtype; the
+    split rows regroup the K sum and are held to the oracle gates.  The automatic choice must land on
+    one of these rows for M <= 32."""
+    from helion_b200 import _lib
+
+    x, y = o.gemm_inputs(m, n, k, seed=900 + m)
+    xd, yd = to_dev(x), to_dev(y)
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        general = hb.fp8_gemm(xd, yd, out_dtype=dt, config=1)
+        swapped = hb.fp8_gemm(xd, yd, out_dtype=dt, config=18)
+        assert torch.equal(general, swapped), f"{m}x{n}x{k} {dt}"
+    check_against_oracle(hb, x, y, torch.bfloat16, config=18)
+    for cfg in (19, 20, None):
+        check_against_oracle(hb, x, y, torch.float32, config=cfg)
+        check_against_oracle(hb, x, y, torch.bfloat16, config=cfg)
+    chosen = _lib.load().hb200_fp8_gemm_select_config(m, n, k, 1, _lib.DT_BF16)
+    assert (chosen in (18, 19, 20)) == (m <= 32)
+    if n % 16 == 0:  # (a row-major y needs N % 16 == 0 to begin with)
+        with pytest.raises(ValueError, match="column-major"):  # these rows are not built for a row-major y
+            hb.fp8_gemm(xd, to_dev(y.contiguous()), config=18)
 
 
 def test_split_k_needs_its_workspace(hb):
