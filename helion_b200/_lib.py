@@ -28,6 +28,7 @@ DT_FP16, DT_BF16, DT_FP32, DT_E4M3 = 0, 1, 2, 3
 OP_GEMM, OP_ATTENTION = 0, 1
 STATIC_SCRATCH_BYTES = 4 << 20
 ATTN_WORKSPACE_BYTES = 16
+SCALE_NONE, SCALE_TENSOR, SCALE_ROWWISE = 0, 1, 2
 
 # Every symbol the header declares, with (restype, argtypes).
 _i64 = ctypes.c_int64
@@ -38,6 +39,11 @@ SIGNATURES = {
         ctypes.c_int,
         [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.c_int, ctypes.c_int, _vp,
          ctypes.c_size_t, ctypes.c_int, _vp],
+    ),
+    "hb200_fp8_gemm_scaled": (
+        ctypes.c_int,
+        [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.c_int, _vp, _vp, ctypes.c_int,
+         ctypes.c_int, _vp, ctypes.c_size_t, ctypes.c_int, _vp],
     ),
     "hb200_fp8_gemm_splitk_static": (
         ctypes.c_int,

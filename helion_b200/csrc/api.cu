@@ -232,9 +232,20 @@ int hb200_fp8_gemm_select_config(int64_t M, int64_t N, int64_t K, int y_is_colma
   return gemm_select_config(M, N, K, y_is_colmajor != 0, out_dtype, 148);
 }
 
-int hb200_fp8_gemm(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K, int64_t x_rs,
-                   int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs, int out_dtype, int cfg_id,
-                   void* workspace, size_t workspace_bytes, int device, void* stream) {
+// Validation and launch shared by hb200_fp8_gemm (scale_mode 0) and hb200_fp8_gemm_scaled.
+static int fp8_gemm_impl(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K, int64_t x_rs,
+                         int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs, int out_dtype, const float* scale_a,
+                         const float* scale_b, int scale_mode, int cfg_id, void* workspace, size_t workspace_bytes,
+                         int device, void* stream) {
+  if (scale_mode != HB200_SCALE_NONE && scale_mode != HB200_SCALE_TENSOR && scale_mode != HB200_SCALE_ROWWISE) {
+    return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm_scaled: scale_mode must be HB200_SCALE_TENSOR or HB200_SCALE_ROWWISE");
+  }
+  if (scale_mode != HB200_SCALE_NONE) {
+    if (scale_a == nullptr || scale_b == nullptr) return set_error(HB200_ERR_ALIGN, "fp8_gemm_scaled: null scale pointer");
+    if ((reinterpret_cast<uintptr_t>(scale_a) | reinterpret_cast<uintptr_t>(scale_b)) & 3u) {
+      return set_error(HB200_ERR_ALIGN, "fp8_gemm_scaled: scale pointers must be 4-byte aligned");
+    }
+  }
   if (out_dtype != HB200_DT_FP16 && out_dtype != HB200_DT_BF16 && out_dtype != HB200_DT_FP32) {
     return set_error(HB200_ERR_BAD_DTYPE, "fp8_gemm: out_dtype must be FP16, BF16 or FP32");
   }
@@ -287,8 +298,29 @@ int hb200_fp8_gemm(const void* x, const void* y, void* out, int64_t M, int64_t N
   a.workspace_bytes = workspace_bytes;
   a.device = device;
   a.stream = static_cast<cudaStream_t>(stream);
+  a.scale_a = scale_a;
+  a.scale_b = scale_b;
+  a.scale_mode = scale_mode;
   DeviceGuard guard(device);
   return launch_fp8_gemm(a, ctx);
+}
+
+int hb200_fp8_gemm(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K, int64_t x_rs,
+                   int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs, int out_dtype, int cfg_id,
+                   void* workspace, size_t workspace_bytes, int device, void* stream) {
+  return fp8_gemm_impl(x, y, out, M, N, K, x_rs, x_cs, y_rs, y_cs, out_rs, out_dtype, nullptr, nullptr,
+                       HB200_SCALE_NONE, cfg_id, workspace, workspace_bytes, device, stream);
+}
+
+int hb200_fp8_gemm_scaled(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K, int64_t x_rs,
+                          int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs, int out_dtype,
+                          const float* scale_a, const float* scale_b, int scale_mode, int cfg_id, void* workspace,
+                          size_t workspace_bytes, int device, void* stream) {
+  if (scale_mode == HB200_SCALE_NONE) {
+    return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm_scaled: scale_mode must be HB200_SCALE_TENSOR or HB200_SCALE_ROWWISE");
+  }
+  return fp8_gemm_impl(x, y, out, M, N, K, x_rs, x_cs, y_rs, y_cs, out_rs, out_dtype, scale_a, scale_b, scale_mode,
+                       cfg_id, workspace, workspace_bytes, device, stream);
 }
 
 int hb200_fp8_gemm_splitk_static(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K,

@@ -21,6 +21,7 @@
 
 #include "common.cuh"
 #include "host.h"
+#include "epilogue.cuh"
 
 namespace hb {
 
@@ -149,7 +150,8 @@ struct StagedStore {
 template <int BN, int STAGES, bool B_MN_MAJOR, int OUT_DT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, void* out,
-                int M, int N, int K, int64_t ldc, int group_m, uint32_t* status, int splits, float* partials) {
+                int M, int N, int K, int64_t ldc, int group_m, uint32_t* status, int splits, float* partials,
+                EpiScale sc) {
   // splits > 1: split-K.  Work unit u = (tile u % num_tiles, K range u / num_tiles); every unit writes
   // its fp32 partial tile to partials[split][M][N] and splitk_reduce_kernel sums and converts.
   using L = GemmLayout<BN, STAGES>;
@@ -314,8 +316,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         const int col0 = tc.n_blk * BN + c;
         if (row < M && col0 < N) {
           if (splits > 1) {
-            store_row_chunk<HB200_DT_FP32>(part, 0, col0, N, r);
+            store_row_chunk<HB200_DT_FP32>(part, 0, col0, N, r);  // unscaled; the reduce pass scales
           } else {
+            scale_chunk(r, sc, row, M, col0, N);
             store_row_chunk<OUT_DT>(out, row_off, col0, N, r);
           }
         }
@@ -338,7 +341,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 // (deterministic).  One thread per 8 consecutive columns.
 template <int OUT_DT>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partials, void* out, int M, int N, int64_t ldc,
-                                     int splits) {
+                                     int splits, EpiScale sc) {
   const int64_t groups_per_row = N / 8;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<int64_t>(M) * groups_per_row) return;
@@ -350,6 +353,11 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partials, void* o
     const float4 a = src[0], b = src[1];
     acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
     acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+  }
+  if (sc.mode != 0) {
+    const float sa = sc.mode == 1 ? __ldg(sc.a) : __ldg(sc.a + row);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = (acc[j] * sa) * (sc.mode == 1 ? __ldg(sc.b) : __ldg(sc.b + col + j));
   }
   if constexpr (OUT_DT == HB200_DT_FP32) {
     float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + row * ldc + col);
@@ -399,7 +407,8 @@ constexpr int PAIR_BN = 256;
 template <int STAGES, bool B_MN_MAJOR, int OUT_DT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                     const __grid_constant__ CUtensorMap tmap_out, int M, int N, int K, int group_m, uint32_t* status) {
+                     const __grid_constant__ CUtensorMap tmap_out, int M, int N, int K, int group_m, uint32_t* status,
+                     EpiScale sc) {
   using L = PairLayout<STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -559,6 +568,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         tmem_ld_32x32b_x32(t_row + c, r);
         tmem_wait_ld();
         const int col = tc.n_blk * PAIR_BN + c;
+        scale_chunk(r, sc, row0 + lane, M, col, N);
         StagedStore<OUT_DT>::store(r, stage, chunk_count, lane, &tmap_out, col, row0, row0 < M && col < N);
       }
       tc_fence_before_sync();
@@ -615,7 +625,7 @@ template <int STAGES, bool B_MN_MAJOR, int OUT_DT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR2_THREADS, 1)
 fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_out, int M, int N, int K, int group_m,
-                      uint32_t* status) {
+                      uint32_t* status, EpiScale sc) {
   using L = Pair2Layout<STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -780,6 +790,7 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         tmem_ld_32x32b_x32(t_row + c, r);
         tmem_wait_ld();
         const int col = tc.n_blk * PAIR2_BN + c;
+        scale_chunk(r, sc, row0 + lane, M, col, N);
         StagedStore<OUT_DT>::store(r, stage, chunk_count, lane, &tmap_out, col, row0, row0 < M && col < N);
       }
       tc_fence_before_sync();
@@ -869,7 +880,7 @@ int launch_pair_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& t
   }
   kernel<<<2 * pairs, NUM_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, tout, static_cast<int>(a.M),
                                                               static_cast<int>(a.N), static_cast<int>(a.K), group_m,
-                                                              ctx->status_dev);
+                                                              ctx->status_dev, epi_scale(a));
   HB_CUDA_CHECK(cudaGetLastError());
   return HB200_OK;
 }
@@ -893,7 +904,7 @@ int launch_pair2_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& 
   }
   kernel<<<2 * pairs, PAIR2_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, tout, static_cast<int>(a.M),
                                                                 static_cast<int>(a.N), static_cast<int>(a.K), group_m,
-                                                                ctx->status_dev);
+                                                                ctx->status_dev, epi_scale(a));
   HB_CUDA_CHECK(cudaGetLastError());
   return HB200_OK;
 }
@@ -958,7 +969,7 @@ int launch_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, co
   const int grid = static_cast<int>(std::min<int64_t>(num_tiles * splits, ctx->num_sms));
   kernel<<<grid, NUM_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, a.out, static_cast<int>(a.M), static_cast<int>(a.N),
                                                          static_cast<int>(a.K), a.ldc, group_m, ctx->status_dev, splits,
-                                                         static_cast<float*>(a.workspace));
+                                                         static_cast<float*>(a.workspace), epi_scale(a));
   HB_CUDA_CHECK(cudaGetLastError());
   return splits > 1 ? launch_splitk_reduce(a, splits) : HB200_OK;
 }
@@ -987,13 +998,13 @@ int launch_splitk_reduce(const GemmArgs& a, int splits) {
   const int m = static_cast<int>(a.M), n = static_cast<int>(a.N);
   switch (a.out_dtype) {
     case HB200_DT_FP16:
-      splitk_reduce_kernel<HB200_DT_FP16><<<blocks, 256, 0, a.stream>>>(partials, a.out, m, n, a.ldc, splits);
+      splitk_reduce_kernel<HB200_DT_FP16><<<blocks, 256, 0, a.stream>>>(partials, a.out, m, n, a.ldc, splits, epi_scale(a));
       break;
     case HB200_DT_BF16:
-      splitk_reduce_kernel<HB200_DT_BF16><<<blocks, 256, 0, a.stream>>>(partials, a.out, m, n, a.ldc, splits);
+      splitk_reduce_kernel<HB200_DT_BF16><<<blocks, 256, 0, a.stream>>>(partials, a.out, m, n, a.ldc, splits, epi_scale(a));
       break;
     case HB200_DT_FP32:
-      splitk_reduce_kernel<HB200_DT_FP32><<<blocks, 256, 0, a.stream>>>(partials, a.out, m, n, a.ldc, splits);
+      splitk_reduce_kernel<HB200_DT_FP32><<<blocks, 256, 0, a.stream>>>(partials, a.out, m, n, a.ldc, splits, epi_scale(a));
       break;
     default:
       return set_error(HB200_ERR_BAD_DTYPE, "fp8_gemm: unsupported out_dtype");

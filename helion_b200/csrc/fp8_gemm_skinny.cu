@@ -21,6 +21,7 @@
 
 #include "common.cuh"
 #include "host.h"
+#include "epilogue.cuh"
 
 namespace hb {
 
@@ -52,7 +53,7 @@ struct SkinnyLayout {
 template <int NM, int OUT_DT>
 __global__ void __launch_bounds__(SK_THREADS, 1)
 fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, void* out,
-                       int M, int N, int K, int64_t ldc, uint32_t* status, int splits, float* partials) {
+                       int M, int N, int K, int64_t ldc, uint32_t* status, int splits, float* partials, EpiScale sc) {
   using L = SkinnyLayout<NM>;
   constexpr int STAGES = L::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -205,11 +206,15 @@ fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
           tmem_wait_ld();
         }
         if (n < N) {
+          // optional scales: this thread's column scale, one row scale per register
+          const bool scaled = sc.mode != 0 && splits == 1;
+          const float sb = scaled ? __ldg(sc.mode == 1 ? sc.b : sc.b + n) : 1.0f;
 #pragma unroll
           for (int i = 0; i < (NM < 32 ? NM : 32); ++i) {
             const int m = c + i;
             if (m < M) {
-              const float v = __uint_as_float(r[i]);
+              float v = __uint_as_float(r[i]);
+              if (scaled) v = (v * __ldg(sc.mode == 1 ? sc.a : sc.a + m)) * sb;
               if (splits > 1) {
                 partials[(static_cast<int64_t>(split) * M + m) * N + n] = v;
               } else if constexpr (OUT_DT == HB200_DT_FP32) {
@@ -252,7 +257,7 @@ int launch_skinny_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap&
   const int grid = static_cast<int>(std::min<int64_t>(n_tiles * splits, ctx->num_sms));
   kernel<<<grid, SK_THREADS, L::SMEM_BYTES, a.stream>>>(tw, tx, a.out, static_cast<int>(a.M), static_cast<int>(a.N),
                                                         static_cast<int>(a.K), a.ldc, ctx->status_dev, splits,
-                                                        static_cast<float*>(a.workspace));
+                                                        static_cast<float*>(a.workspace), epi_scale(a));
   HB_CUDA_CHECK(cudaGetLastError());
   return HB200_OK;
 }

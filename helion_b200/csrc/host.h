@@ -78,6 +78,10 @@ struct GemmArgs {
   size_t workspace_bytes;
   int device;
   cudaStream_t stream;
+  // optional output scales (hb200_fp8_gemm_scaled): HB200_SCALE_NONE / _TENSOR / _ROWWISE
+  const float* scale_a = nullptr;
+  const float* scale_b = nullptr;
+  int scale_mode = 0;
 };
 
 int launch_fp8_gemm(const GemmArgs& args, DeviceCtx* ctx);

@@ -46,6 +46,8 @@ def fp8_gemm(
     out_dtype: torch.dtype = torch.float16,
     config: Optional[int] = None,
     out: Optional[torch.Tensor] = None,
+    scale_a: Optional[torch.Tensor] = None,
+    scale_b: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """``out = (x @ y).to(out_dtype)`` for float8_e4m3fn ``x [M,K]`` and ``y [K,N]``, fp32 accumulation.
 
@@ -53,6 +55,11 @@ def fp8_gemm(
     default.  ``y`` may be row-major or column-major (a transposed view); ``x`` must be row-major.
     ``out_dtype`` (fp16 / bf16 / fp32), ``config`` (tile-config id, None = table choice) and ``out``
     are keyword-only extensions.
+
+    ``scale_a`` / ``scale_b`` (fp32 CUDA tensors, both or neither) give
+    ``out = (((x @ y) * scale_a) * scale_b).to(out_dtype)`` with the shapes ``torch._scaled_mm``
+    accepts: one element each (per-tensor), or ``[M, 1]`` / ``[M]`` and ``[1, N]`` / ``[N]``
+    (row-wise).  The reference fixes both at 1.0 (examples/fp8_gemm.py:74-75).
     """
     if x.dtype != torch.float8_e4m3fn or y.dtype != torch.float8_e4m3fn:
         raise TypeError(f"fp8_gemm expects float8_e4m3fn inputs, got {x.dtype} and {y.dtype}")
@@ -83,14 +90,41 @@ def fp8_gemm(
     # from torch's caching allocator and is only used by this call's two kernels on this stream.
     ws_bytes = lib.hb200_fp8_gemm_workspace_bytes(m, n, k, _OUT_DT[out_dtype], cfg)
     workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
-    code = lib.hb200_fp8_gemm(
-        x.data_ptr(), y.data_ptr(), out.data_ptr(), m, n, k,
-        x.stride(0), x.stride(1), y.stride(0), y.stride(1), out.stride(0),
-        _OUT_DT[out_dtype], cfg,
-        workspace.data_ptr() if workspace is not None else None, ws_bytes, dev, _stream_ptr(dev),
-    )
+    ws_ptr = workspace.data_ptr() if workspace is not None else None
+    if scale_a is None and scale_b is None:
+        code = lib.hb200_fp8_gemm(
+            x.data_ptr(), y.data_ptr(), out.data_ptr(), m, n, k,
+            x.stride(0), x.stride(1), y.stride(0), y.stride(1), out.stride(0),
+            _OUT_DT[out_dtype], cfg, ws_ptr, ws_bytes, dev, _stream_ptr(dev),
+        )
+    else:
+        sa, sb, mode = _check_scales(scale_a, scale_b, m, n, x.device)
+        code = lib.hb200_fp8_gemm_scaled(
+            x.data_ptr(), y.data_ptr(), out.data_ptr(), m, n, k,
+            x.stride(0), x.stride(1), y.stride(0), y.stride(1), out.stride(0),
+            _OUT_DT[out_dtype], sa.data_ptr(), sb.data_ptr(), mode, cfg, ws_ptr, ws_bytes, dev, _stream_ptr(dev),
+        )
     _lib.raise_for(code, "fp8_gemm")
     return out
+
+
+def _check_scales(scale_a, scale_b, m: int, n: int, device):
+    """Validate the two scale tensors; returns contiguous fp32 tensors and the C-ABI scale mode."""
+    if scale_a is None or scale_b is None:
+        raise ValueError("fp8_gemm: pass both scale_a and scale_b or neither")
+    for name, t in (("scale_a", scale_a), ("scale_b", scale_b)):
+        if not isinstance(t, torch.Tensor) or t.dtype != torch.float32:
+            raise TypeError(f"fp8_gemm: {name} must be a float32 tensor")
+        if t.device != device:
+            raise ValueError(f"fp8_gemm: {name} must live on the inputs' device")
+    if scale_a.numel() == 1 and scale_b.numel() == 1:
+        return scale_a.reshape(1).contiguous(), scale_b.reshape(1).contiguous(), _lib.SCALE_TENSOR
+    if tuple(scale_a.shape) in ((m, 1), (m,)) and tuple(scale_b.shape) in ((1, n), (n,)):
+        return scale_a.reshape(m).contiguous(), scale_b.reshape(n).contiguous(), _lib.SCALE_ROWWISE
+    raise ValueError(
+        f"fp8_gemm: scales must be one element each, or [M,1]/[M] and [1,N]/[N]; got {tuple(scale_a.shape)} and "
+        f"{tuple(scale_b.shape)} for M={m}, N={n}"
+    )
 
 
 def fp8_attention(

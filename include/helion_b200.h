@@ -72,6 +72,25 @@ HB200_API int hb200_fp8_gemm(const void* x, const void* y, void* out, int64_t M,
                    int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs, int out_dtype, int cfg_id,
                    void* workspace, size_t workspace_bytes, int device, void* stream);
 
+/* hb200_fp8_gemm with output scales: out = cast(((x @ y) * scale_a) * scale_b), the two
+ * multiplications in fp32 on the fp32 accumulator, in that order, before the cast.  The reference
+ * hard-codes unit scales (examples/fp8_gemm.py:74-75 and helion/language/matmul_ops.py:232-233 pass
+ * torch.tensor(1.0) as scale_a and scale_b of torch._scaled_mm); callers with real FP8 tensors carry
+ * scales, and this entry point takes the two forms torch._scaled_mm takes:
+ *   HB200_SCALE_TENSOR:  scale_a and scale_b point to ONE float each (per-tensor scales);
+ *   HB200_SCALE_ROWWISE: scale_a points to M floats (one per row of x / out), scale_b to N floats
+ *                        (one per column of y / out).
+ * The scales are device pointers to fp32, read when the kernel runs.  All other arguments and
+ * limits are those of hb200_fp8_gemm; with unit scales the result equals hb200_fp8_gemm's bit for
+ * bit. */
+#define HB200_SCALE_NONE 0
+#define HB200_SCALE_TENSOR 1
+#define HB200_SCALE_ROWWISE 2
+HB200_API int hb200_fp8_gemm_scaled(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K,
+                          int64_t x_rs, int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs, int out_dtype,
+                          const float* scale_a, const float* scale_b, int scale_mode, int cfg_id, void* workspace,
+                          size_t workspace_bytes, int device, void* stream);
+
 /* Bytes of workspace hb200_fp8_gemm needs for this problem and configuration (0 for most). */
 HB200_API size_t hb200_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int cfg_id);
 

@@ -150,6 +150,44 @@ def test_few_rows_of_x_use_the_operand_swapped_kernel(hb, m, n, k):
             hb.fp8_gemm(xd, to_dev(y.contiguous()), config=18)
 
 
+@pytest.mark.parametrize(
+    "m,n,k,config",
+    [(200, 272, 1152, 1), (200, 272, 1152, 0), (520, 784, 256, 6), (600, 528, 384, 14), (16, 2000, 528, 18),
+     (16, 2000, 528, 20), (100, 272, 1152, 12), (300, 520, 640, None), (7, 136, 64, None)],
+)
+def test_output_scales(hb, m, n, k, config):
+    """hb200_fp8_gemm_scaled: per-tensor and row-wise scales multiply the fp32 accumulator in the
+    epilogue of every kernel family (single-CTA, CTA pair, 512-row pair, operand-swapped, split-K
+    reduce).  Against the oracle with the same order of the two multiplications the fp32 result may
+    differ only by the order of the K sum (allclose 1e-5 relative to the largest output); with unit
+    scales and with power-of-two scales the unscaled kernel must be reproduced bit for bit."""
+    x, y = o.gemm_inputs(m, n, k, seed=300 + m)
+    xd, yd = to_dev(x), to_dev(y)
+    xb, yb = o.torch_fp8_to_bits(x), o.torch_fp8_to_bits(y)
+    plain = hb.fp8_gemm(xd, yd, out_dtype=torch.float32, config=config)
+    one = torch.ones(1, device="cuda")
+    assert torch.equal(hb.fp8_gemm(xd, yd, out_dtype=torch.float32, config=config, scale_a=one, scale_b=one), plain)
+    quarter, eight = torch.full((m, 1), 0.25, device="cuda"), torch.full((1, n), 8.0, device="cuda")
+    assert torch.equal(hb.fp8_gemm(xd, yd, out_dtype=torch.float32, config=config, scale_a=quarter, scale_b=eight),
+                       plain * 2.0)
+    g = torch.Generator().manual_seed(m)
+    sa_t, sb_t = torch.tensor([0.37]), torch.tensor([2.5])
+    sa_r = torch.rand(m, 1, generator=g) + 0.5
+    sb_r = torch.rand(1, n, generator=g) * 2.0 + 0.25
+    for sa, sb in ((sa_t, sb_t), (sa_r, sb_r)):
+        for dt in (torch.float32, torch.bfloat16, torch.float16):
+            got = hb.fp8_gemm(xd, yd, out_dtype=dt, config=config, scale_a=sa.cuda(), scale_b=sb.cuda())
+            want = o.fp8_gemm_scaled(xb, yb, sa.numpy(), sb.numpy(), DT_NAME[dt])
+            tol = 1e-5 * float(np.abs(want).max()) if dt == torch.float32 else 2e-2
+            np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=1e-5 if dt == torch.float32 else 2e-2, atol=tol)
+    with pytest.raises(ValueError, match="both scale_a and scale_b"):
+        hb.fp8_gemm(xd, yd, scale_a=one)
+    with pytest.raises(ValueError, match="scales must be"):
+        hb.fp8_gemm(xd, yd, scale_a=torch.ones(m + 1, device="cuda"), scale_b=torch.ones(n, device="cuda"))
+    with pytest.raises(TypeError, match="float32"):
+        hb.fp8_gemm(xd, yd, scale_a=one.half(), scale_b=one)
+
+
 def test_split_k_needs_its_workspace(hb):
     from helion_b200 import _lib
 

@@ -100,3 +100,27 @@ def test_input_generators_are_seeded_and_in_range():
     assert not torch.isnan(y1.float()).any()
     _, w = o.gemm_inputs(64, 48, 32, seed=5, weight_like=True)
     assert w.float().abs().max() == 448.0
+
+
+def test_scaled_gemm_oracle_against_aten_and_its_own_identities():
+    """The op the reference calls is ATen's _scaled_mm (examples/fp8_gemm.py:74-78, with both scales
+    1.0).  Its CPU build takes per-tensor scales: the restatement must agree with it to fp32
+    rounding.  Row-wise scales exist only in ATen's CUDA build, so that form is pinned by
+    identities: constant vectors equal the per-tensor form bit for bit, unit scales equal the
+    unscaled oracle, and powers of two commute with every rounding."""
+    x, y = o.gemm_inputs(48, 80, 64, seed=21)
+    xb, yb = o.torch_fp8_to_bits(x), o.torch_fp8_to_bits(y)
+    sa, sb = np.float32(0.37), np.float32(2.5)
+    want = torch._scaled_mm(x, y, torch.tensor(float(sa)), torch.tensor(float(sb)), out_dtype=torch.float32).numpy()
+    got = o.fp8_gemm_scaled(xb, yb, sa, sb, "fp32")
+    np.testing.assert_allclose(got, want, rtol=2e-6, atol=1e-5)
+    rows = o.fp8_gemm_scaled(xb, yb, np.full(48, sa), np.full(80, sb), "fp32")
+    assert np.array_equal(rows, got)
+    assert np.array_equal(o.fp8_gemm_scaled(xb, yb, 1.0, 1.0, "bf16"), o.fp8_gemm(xb, yb, "bf16"))
+    assert np.array_equal(o.fp8_gemm_scaled(xb, yb, 0.25, 8.0, "fp32"), 2.0 * o.fp8_gemm(xb, yb, "fp32"))
+    ra = np.linspace(0.5, 1.5, 48, dtype=np.float32)
+    rb = np.linspace(2.0, 0.25, 80, dtype=np.float32)
+    full = o.fp8_gemm(xb, yb, "fp32")
+    np.testing.assert_array_equal(o.fp8_gemm_scaled(xb, yb, ra, rb, "fp32"), (full * ra[:, None]) * rb[None, :])
+    with pytest.raises(ValueError):
+        o.fp8_gemm_scaled(xb, yb, ra, np.float32(1.0), "fp32")
