@@ -55,6 +55,9 @@ def preprocess_fp8_attention_inputs(
     the returned ``v`` is a [BH, D, S] view of memory that is physically [BH, S, D]; the CUDA
     kernel reads either layout without a copy.
     """
+    if q.is_cuda and q.dtype == k.dtype == v.dtype and q.dtype in (torch.float16, torch.bfloat16, torch.float32):
+        # the three casts as one CUDA kernel (hb200_fp8_attention_preprocess)
+        return _ops.preprocess_fp8_attention_inputs(q, k, v)
     q_fp8 = q.to(torch.float8_e4m3fn)
     k_fp8 = k.to(torch.float8_e4m3fn)
     v_fp8 = v.permute(0, 1, 3, 2).to(torch.float8_e4m3fn)

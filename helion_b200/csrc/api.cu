@@ -475,6 +475,27 @@ int hb200_fp8_attention(const void* q, const void* k, const void* v, void* out, 
                             out_dtype, cfg_id, nullptr, 0, device, stream);
 }
 
+int hb200_fp8_attention_preprocess(const void* q, const void* k, const void* v, void* q8, void* k8, void* v8,
+                                   int64_t count, int src_dtype, int device, void* stream) {
+  if (src_dtype != HB200_DT_FP16 && src_dtype != HB200_DT_BF16 && src_dtype != HB200_DT_FP32) {
+    return set_error(HB200_ERR_BAD_DTYPE, "fp8_attention_preprocess: source dtype must be FP16, BF16 or FP32");
+  }
+  if (count < 1 || count % 16 != 0) {
+    return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention_preprocess: the element count must be a positive multiple of 16");
+  }
+  if (q == nullptr || k == nullptr || v == nullptr || q8 == nullptr || k8 == nullptr || v8 == nullptr) {
+    return set_error(HB200_ERR_ALIGN, "fp8_attention_preprocess: null pointer");
+  }
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(q8) | reinterpret_cast<uintptr_t>(k8) | reinterpret_cast<uintptr_t>(v8)) & 15u) {
+    return set_error(HB200_ERR_ALIGN, "fp8_attention_preprocess: all six tensors must be 16-byte aligned");
+  }
+  DeviceCtx* ctx = get_device_ctx(device);
+  if (ctx == nullptr) return ctx_error_code(device);
+  DeviceGuard guard(device);
+  return launch_attention_preprocess(q, k, v, q8, k8, v8, count, src_dtype, ctx, static_cast<cudaStream_t>(stream));
+}
+
 int hb200_fp8_attention_ws(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S, int64_t D,
                            const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
                            const int64_t out_strides[3], float scale_log2, int out_dtype, int cfg_id, void* workspace,

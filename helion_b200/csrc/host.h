@@ -121,6 +121,9 @@ struct AttnArgs {
 };
 
 int launch_fp8_attention(const AttnArgs& args, DeviceCtx* ctx);
+// q, k, v (fp16 / bf16 / fp32, `count` elements each) -> e4m3fn with torch's cast rule (quantize.cu).
+int launch_attention_preprocess(const void* q, const void* k, const void* v, void* q8, void* k8, void* v8, int64_t count,
+                                int src_dtype, DeviceCtx* ctx, cudaStream_t stream);
 int attn_num_configs();
 int attn_describe_config(int cfg_id, char* buf, int buf_len);
 

@@ -218,3 +218,35 @@ def attention_into(
             scale_log2, _OUT_DT[out3.dtype], cfg, dev, _stream_ptr(dev),
         )
     _lib.raise_for(code, "fp8_attention")
+
+
+def preprocess_fp8_attention_inputs(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``[B,H,S,D]`` fp16 / bf16 / fp32 tensors -> e4m3 ``q [BH,S,D]``, ``k [BH,S,D]``, ``v [BH,D,S]``.
+
+    Same results, shapes and strides as the reference's function of this name
+    (examples/fp8_attention.py:110-133), whose three ``.to(float8_e4m3fn)`` casts run here as one
+    CUDA kernel; ``v`` comes back as the reference's pre-transposed view of memory that is physically
+    ``[BH, S, D]``.  Inputs that are already e4m3 are only reshaped.
+    """
+    if q.dim() != 4 or q.shape != k.shape or q.shape != v.shape:
+        raise ValueError(f"expected three [B,H,S,D] tensors, got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    batch, heads, seq, dim = q.shape
+    bh = batch * heads
+    if q.dtype == k.dtype == v.dtype == torch.float8_e4m3fn:
+        q8, k8, v8 = q.contiguous(), k.contiguous(), v.contiguous()
+    else:
+        if not (q.dtype == k.dtype == v.dtype) or q.dtype not in _OUT_DT or q.dtype == torch.float8_e4m3fn:
+            raise TypeError(f"q, k, v must share one dtype of float16, bfloat16, float32; got {q.dtype}, {k.dtype}, {v.dtype}")
+        dev = _require_cuda(q, k, v)
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        q8, k8, v8 = (torch.empty(t.shape, dtype=torch.float8_e4m3fn, device=t.device) for t in (q, k, v))
+        count = q.numel()
+        if count:
+            code = _lib.load().hb200_fp8_attention_preprocess(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), q8.data_ptr(), k8.data_ptr(), v8.data_ptr(), count,
+                _OUT_DT[q.dtype], dev, _stream_ptr(dev),
+            )
+            _lib.raise_for(code, "preprocess_fp8_attention_inputs")
+    return q8.reshape(bh, seq, dim), k8.reshape(bh, seq, dim), v8.reshape(bh, seq, dim).permute(0, 2, 1)

@@ -135,6 +135,17 @@ HB200_API int hb200_fp8_attention_ws(const void* q, const void* k, const void* v
                            int out_dtype, int cfg_id, void* workspace, size_t workspace_bytes, int device,
                            void* stream);
 
+/* q, k, v -> float8_e4m3fn in one launch: the three casts of preprocess_fp8_attention_inputs
+ * (examples/fp8_attention.py:125-128; the permute and reshapes of :127-132 only change strides, so
+ * the caller does them as views).  Each of q, k, v holds `count` contiguous elements of src_dtype
+ * (HB200_DT_FP16, HB200_DT_BF16 or HB200_DT_FP32); q8, k8, v8 receive `count` bytes each, element
+ * i of the output being the cast of element i of the input.  The cast is torch's
+ * Tensor.to(torch.float8_e4m3fn): round to nearest even; a value that rounds beyond +-448, an
+ * infinity or a NaN becomes the NaN pattern (no saturation).  count % 16 == 0; all pointers are
+ * 16-byte aligned device pointers. */
+HB200_API int hb200_fp8_attention_preprocess(const void* q, const void* k, const void* v, void* q8, void* k8, void* v8,
+                                   int64_t count, int src_dtype, int device, void* stream);
+
 /* Split-K FP8 GEMM that allocates nothing: same computation and arguments as hb200_fp8_gemm with a
  * split-K row of the table, but the fp32 partial sums live in a fixed array compiled into the
  * library instead of a caller-provided workspace.  It has no counterpart in the reference; it
