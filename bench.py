@@ -466,10 +466,26 @@ def make_workload(name: str, torch, dev, hb, config=None):
         outm = torch.empty(m, MLP_N, dtype=torch.bfloat16, device=dev)
         return (lambda: hb.fp8_gemm(xa, w, out_dtype=torch.bfloat16, out=outm, config=config),
                 2.0 * m * MLP_N * MLP_K, m * MLP_K + MLP_K * MLP_N + 2 * m * MLP_N)
+    if name == "gemm_8192_rowwise_scaled":  # hb200_fp8_gemm_scaled: one scale per row of x and per column of y
+        g = torch.Generator(device=dev).manual_seed(1)
+        xa = torch.randn(M, K, device=dev, generator=g).to(torch.float8_e4m3fn)
+        ya = torch.randn(N, K, device=dev, generator=g).to(torch.float8_e4m3fn).t()
+        sa = torch.rand(M, 1, device=dev, generator=g) + 0.5
+        sb = torch.rand(1, N, device=dev, generator=g) + 0.5
+        outg = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        return (lambda: hb.fp8_gemm(xa, ya, out_dtype=torch.bfloat16, out=outg, config=config, scale_a=sa, scale_b=sb),
+                GEMM_FLOPS, M * K + K * N + 2 * M * N + 4 * (M + N))
+    if name.startswith("preprocess_"):  # q, k, v fp16 -> e4m3 in one launch (hb200_fp8_attention_preprocess)
+        b, h, s, d = ATTN_SHAPES["attn_" + name[len("preprocess_"):]]
+        g = torch.Generator(device=dev).manual_seed(4)
+        q, k, v = (torch.randn(b, h, s, d, device=dev, generator=g, dtype=torch.float16) for _ in range(3))
+        return (lambda: hb.preprocess_fp8_attention_inputs(q, k, v), 0.0, 3 * b * h * s * d * (2 + 1))
     raise SystemExit(f"unknown workload {name!r}")
 
 
-WORKLOADS = ["gemm_8192", *ATTN_SHAPES, *(f"mlp_M{m}" for m in MLP_M), "cublaslt_8192"]
+PREPROCESS = [f"preprocess_{n[len('attn_'):]}" for n in ATTN_SHAPES]
+WORKLOADS = ["gemm_8192", *ATTN_SHAPES, *(f"mlp_M{m}" for m in MLP_M), "cublaslt_8192", "gemm_8192_rowwise_scaled",
+             *PREPROCESS]
 
 
 def run_only(args, torch, dev, hb, _lib, emit) -> None:
@@ -502,6 +518,13 @@ def run_extras(hb, _lib, o, torch, dev, flush, fp8_peak, peaks) -> dict:
 
     res["attention"] = {name: entry(name) for name in ATTN_SHAPES}
     res["mlp_K4096_N14336"] = {f"M{m}": entry(f"mlp_M{m}") for m in MLP_M}
+    # the callers either side of the two kernels: scaled GEMM epilogue, attention input preparation
+    res["gemm_8192_rowwise_scaled"] = entry("gemm_8192_rowwise_scaled")
+    res["attention_preprocess_fp16"] = {}
+    for name in PREPROCESS:
+        e = entry(name)
+        res["attention_preprocess_fp16"][name] = {"ms": e["ms"], "hbm_gbs": e["hbm_gbs"],
+                                                  "frac_of_measured_hbm": e["frac_of_measured_hbm"]}
 
     # cuBLASLt on the same workload, for context (the reference's GPU baseline, examples/fp8_gemm.py:61-78)
     try:

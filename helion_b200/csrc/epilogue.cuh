@@ -24,10 +24,23 @@ __device__ __forceinline__ void scale_chunk(uint32_t (&r)[32], const EpiScale& s
     for (int i = 0; i < 32; ++i) r[i] = __float_as_uint((__uint_as_float(r[i]) * sa) * sb);
   } else {
     const float sa = row < M ? __ldg(sc.a + row) : 0.0f;
+    const float* pb = sc.b + col0;
+    if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(pb) & 15u) == 0) {
+      // the common case: eight 16-byte loads (the same addresses in every lane, so one broadcast each)
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float sb = col0 + i < N ? __ldg(sc.b + col0 + i) : 0.0f;
-      r[i] = __float_as_uint((__uint_as_float(r[i]) * sa) * sb);
+      for (int i = 0; i < 8; ++i) {
+        const float4 b4 = __ldg(reinterpret_cast<const float4*>(pb) + i);
+        r[4 * i] = __float_as_uint((__uint_as_float(r[4 * i]) * sa) * b4.x);
+        r[4 * i + 1] = __float_as_uint((__uint_as_float(r[4 * i + 1]) * sa) * b4.y);
+        r[4 * i + 2] = __float_as_uint((__uint_as_float(r[4 * i + 2]) * sa) * b4.z);
+        r[4 * i + 3] = __float_as_uint((__uint_as_float(r[4 * i + 3]) * sa) * b4.w);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float sb = col0 + i < N ? __ldg(pb + i) : 0.0f;
+        r[i] = __float_as_uint((__uint_as_float(r[i]) * sa) * sb);
+      }
     }
   }
 }
