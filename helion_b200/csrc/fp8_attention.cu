@@ -12,10 +12,12 @@
 // the last partial round.  Tile ids reach the other roles through a two-entry queue in shared
 // memory that rides on the Q barriers; -1 ends the kernel.
 //
-//   warp 0      TMA producer: Q tile, then K/V tiles through one ring of smem slots
-//   warp 1      MMA issuer (one thread): S = Q K^T into tensor memory, then O += P V with P read
-//               from shared memory; tcgen05.commit publishes S / frees slots / publishes O
-//   warp 2      tensor-memory allocation
+//   one warp    TMA producer: Q tile, then K/V tiles through one ring of smem slots
+//   one warp    MMA thread 1: S = Q K^T into tensor memory; tcgen05.commit publishes S and frees K slots
+//   one warp    MMA thread 2: O += P V with P read from shared memory; tcgen05.commit frees V slots
+//               and publishes O.  (Which of warps 0-3 takes which role depends on which of the SM's
+//               CTAs this is, so that the MMA threads of co-resident CTAs sit on different schedulers.)
+//   warp 2      also allocates and frees the tensor memory
 //   warps 4-7   softmax: each thread owns one query row: pulls its 128 scores out of tensor memory
 //               into registers (which frees S for the next Q K^T at once), row max, exp2, row sum,
 //               e4m3 P into 128B-swizzled smem, rescales O in tensor memory when the max moved,
@@ -52,7 +54,7 @@ struct AttnLayout {
   static constexpr int KV_OFFSET = P_OFFSET + ATT_BM * BN;
   static constexpr int BAR_OFFSET = KV_OFFSET + KV_STAGES * TILE_BYTES;
   // q_full q_empty s_full s_free p_full pv_done drain kv_full[ST] kv_empty[ST]
-  static constexpr int NUM_BARS = 7 + 2 * KV_STAGES;
+  static constexpr int NUM_BARS = 8 + 2 * KV_STAGES;  // + drain of the second MMA thread, last
   static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = MISC_OFFSET + 16 + 1024;
   static_assert(SMEM_BYTES <= (CTAS_PER_SM == 4 ? 56 : 113) * 1024, "the CTAs must fit one SM together");
@@ -99,6 +101,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint64_t* drain = bars + 6;
   uint64_t* kv_full = bars + 7;
   uint64_t* kv_empty = bars + 7 + ST;
+  uint64_t* drain_pv = bars + 7 + 2 * ST;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFFSET + 4);
   volatile int* tile_q = reinterpret_cast<volatile int*>(smem + L::MISC_OFFSET + 8);  // [2], indexed by tile parity
@@ -112,12 +115,14 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(q_empty, 1 + ATT_SOFTMAX_THREADS);  // last Q K^T of the tile + every softmax thread has the tile id
+    // last Q K^T of the tile + every softmax thread and the P V thread have the tile id
+    mbar_init(q_empty, 2 + ATT_SOFTMAX_THREADS);
     mbar_init(s_full, 1);
     mbar_init(s_free, ATT_SOFTMAX_THREADS);
     mbar_init(p_full, ATT_SOFTMAX_THREADS);
     mbar_init(pv_done, 1);
     mbar_init(drain, 1);
+    mbar_init(drain_pv, 1);
     for (int s = 0; s < ST; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
@@ -135,9 +140,17 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Which warp plays which role depends on which of the SM's CTAs this is (read off the tensor-memory
+  // columns it was given): issuing a tcgen05 instruction occupies its scheduler for tens of cycles, and
+  // every scheduler also hosts one softmax warp of each resident CTA, so the two MMA threads of the
+  // two CTAs are spread over all four schedulers instead of loading one of them with everything.
+  const uint32_t sm_slot = ((tmem_base & 0xffffu) / ATT_TMEM_COLS) & 1u;
+  const int w_producer = sm_slot ? 1 : 0;
+  const int w_qk = sm_slot ? 2 : 1;
+  const int w_pv = sm_slot ? 0 : 3;
   if (warp < 4) {
     reg_dec_wg0<L::CTAS_PER_SM>();
-    if (warp == 0) {
+    if (warp == w_producer) {
       // ------------------------------- TMA producer ------------------------------------------
       if (lane == 0) {
         tma_prefetch_desc(&tmap_q);
@@ -195,58 +208,72 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
       __syncwarp();
-    } else if (warp == 1) {
-      // ------------------------------- MMA issuer --------------------------------------------
+    } else if (warp == w_qk) {
+      // ------------------------------- MMA thread 1: S = Q K^T -------------------------------
       if (lane == 0) {
         constexpr uint32_t idesc_qk = make_idesc_e4m3(ATT_BM, ATT_BN, false, false);
-        constexpr uint32_t idesc_pv = make_idesc_e4m3(ATT_BM, D, false, !V_KMAJOR);
         const uint32_t q_addr = smem_u32(smem + L::Q_OFFSET);
-        const uint32_t p_addr = smem_u32(smem + L::P_OFFSET);
         const uint32_t kv_addr = smem_u32(smem + L::KV_OFFSET);
         const uint32_t t_s = tmem_base;
-        const uint32_t t_o = tmem_base + ATT_O_COL;
         const uint64_t q_desc = make_smem_desc(q_addr, 16, SBO_QK, SWZ_QK);
-        const uint64_t p_desc = make_smem_desc(p_addr, 16, SBO_P, SWZ_P);
-        uint32_t g = 0;        // running step counter: phases of s_full / s_free / p_full / pv_done
-        uint32_t slot_it = 0;  // ring position of the K tile of the step whose Q K^T is issued next
+        uint32_t g = 0;        // running step counter: phases of s_full / s_free
+        uint32_t slot_it = 0;  // ring position of this step's K tile (its V tile is the next one)
         uint32_t tile_iter = 0;
         bool ok = true;
-
-        // Q K^T of one step: waits for the K tile (and for S to be free), issues D/32 MMAs.
-        auto issue_qk = [&](uint32_t k_slot_it, uint32_t step_g, bool last_of_tile) -> bool {
-          const uint32_t s = k_slot_it % ST;
-          if (!mbar_wait_relaxed(&kv_full[s], (k_slot_it / ST) & 1u, wctx, SITE_ATTN_K_FULL, 100)) return false;
-          if (step_g > 0 && !mbar_wait_relaxed(s_free, (step_g - 1u) & 1u, wctx, SITE_ATTN_S_FREE, 100)) return false;
-          tc_fence_after_sync();
-          const uint64_t k_desc = make_smem_desc(kv_addr + s * L::TILE_BYTES, 16, SBO_QK, SWZ_QK);
-#pragma unroll
-          for (int k = 0; k < D / 32; ++k) {
-            umma_f8_ss(t_s, desc_advance(q_desc, k * 32), desc_advance(k_desc, k * 32), idesc_qk, k != 0 ? 1u : 0u);
-          }
-          umma_commit(&kv_empty[s]);
-          if (last_of_tile) umma_commit(q_empty);
-          umma_commit(s_full);
-          return true;
-        };
-
         for (; ok; ++tile_iter) {
           if (!mbar_wait_relaxed(q_full, tile_iter & 1u, wctx, SITE_ATTN_Q, 100)) {
             ok = false;
             break;
           }
           if (tile_q[tile_iter & 1u] < 0) break;  // no more tiles
-          if (!issue_qk(slot_it, g, n_steps == 1)) {
+          for (int j = 0; j < n_steps; ++j, ++g, slot_it += 2) {
+            // waits for the K tile and for S to be free (the softmax warps have pulled step g-1 out)
+            const uint32_t s = slot_it % ST;
+            if (!mbar_wait_relaxed(&kv_full[s], (slot_it / ST) & 1u, wctx, SITE_ATTN_K_FULL, 100) ||
+                (g > 0 && !mbar_wait_relaxed(s_free, (g - 1u) & 1u, wctx, SITE_ATTN_S_FREE, 100))) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint64_t k_desc = make_smem_desc(kv_addr + s * L::TILE_BYTES, 16, SBO_QK, SWZ_QK);
+#pragma unroll
+            for (int k = 0; k < D / 32; ++k) {
+              umma_f8_ss(t_s, desc_advance(q_desc, k * 32), desc_advance(k_desc, k * 32), idesc_qk, k != 0 ? 1u : 0u);
+            }
+            umma_commit(&kv_empty[s]);
+            if (j + 1 == n_steps) umma_commit(q_empty);
+            umma_commit(s_full);
+          }
+        }
+        if (!ok) {
+          umma_commit(drain);
+          mbar_drain(drain, 0);
+        }
+      }
+      __syncwarp();
+    } else if (warp == w_pv) {
+      // ------------------------------- MMA thread 2: O (+)= P V ------------------------------
+      // Ordered against thread 1 by the barriers alone: P V of step g starts after p_full(g), which
+      // the softmax warps signal after pv_done(g-1); Q K^T of step g+1 only touches S.
+      if (lane == 0) {
+        constexpr uint32_t idesc_pv = make_idesc_e4m3(ATT_BM, D, false, !V_KMAJOR);
+        const uint32_t p_addr = smem_u32(smem + L::P_OFFSET);
+        const uint32_t kv_addr = smem_u32(smem + L::KV_OFFSET);
+        const uint32_t t_o = tmem_base + ATT_O_COL;
+        const uint64_t p_desc = make_smem_desc(p_addr, 16, SBO_P, SWZ_P);
+        uint32_t g = 0;        // running step counter: phases of p_full / pv_done
+        uint32_t slot_it = 0;  // ring position of this step's K tile; V is slot_it + 1
+        uint32_t tile_iter = 0;
+        bool ok = true;
+        for (; ok; ++tile_iter) {
+          if (!mbar_wait_relaxed(q_full, tile_iter & 1u, wctx, SITE_ATTN_Q, 100)) {
             ok = false;
             break;
           }
+          const int tile = tile_q[tile_iter & 1u];
+          mbar_arrive(q_empty);  // this thread has the id (keeps q_full from running two phases ahead of it)
+          if (tile < 0) break;
           for (int j = 0; j < n_steps; ++j, ++g, slot_it += 2) {
-            if (j + 1 < n_steps) {
-              if (!issue_qk(slot_it + 2, g + 1, j + 2 == n_steps)) {
-                ok = false;
-                break;
-              }
-            }
-            // O (+)= P V
             const uint32_t vs = (slot_it + 1) % ST;
             if (!mbar_wait_relaxed(&kv_full[vs], ((slot_it + 1) / ST) & 1u, wctx, SITE_ATTN_V_FULL, 100) ||
                 !mbar_wait_relaxed(p_full, g & 1u, wctx, SITE_ATTN_P_FULL, 100)) {
@@ -270,8 +297,8 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           }
         }
         if (!ok) {
-          umma_commit(drain);
-          mbar_drain(drain, 0);
+          umma_commit(drain_pv);
+          mbar_drain(drain_pv, 0);
         }
       }
       __syncwarp();
