@@ -1,0 +1,104 @@
+"""FP8 GEMM on HOST buffers: pinned x, y in, pinned out back, with the PCIe copies overlapped.
+
+A caller whose operands live in host memory pays for three transfers per GEMM (x and y in, out
+back); done one after the other on one stream they take ~15x longer than the 8192^3 GEMM itself.
+:class:`HostGemm` runs them as a pipeline instead:
+
+* three CUDA streams -- copy-in, compute, copy-out -- so that host->device and device->host
+  traffic (PCIe is full duplex) and the kernels overlap;
+* x and out are cut into row blocks: block i is multiplied while block i+1 is still arriving and
+  block i-1 is already on its way back (row blocks of a GEMM are independent, the same fact the
+  multi-GPU sharding uses);
+* the device buffers exist ``depth`` times, so the next call's uploads overlap this call's
+  downloads.
+
+The arithmetic is that of :func:`helion_b200.ops.fp8_gemm` on every row block, so the result is
+bit-identical to one call on the whole matrix.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from . import ops
+
+
+class HostGemm:
+    """Pipeline for ``out_host = (x_host @ y_host).to(out_dtype)`` with e4m3 operands in pinned memory.
+
+    ``x_host``: uint8 or float8_e4m3fn ``[M, K]`` row-major; ``y_host``: ``[N, K]`` bytes, i.e. ``y``
+    stored column-major (the layout the benchmark configurations and ``torch._scaled_mm`` use);
+    ``out_host``: ``[M, N]`` of ``out_dtype``.  All three must be pinned for the copies to be
+    asynchronous.
+    """
+
+    def __init__(self, m: int, n: int, k: int, *, out_dtype: torch.dtype = torch.bfloat16, device=None,
+                 row_blocks: int = 8, depth: int = 2) -> None:
+        if not torch.cuda.is_available():
+            raise RuntimeError("HostGemm needs a CUDA device; there is no CPU path")
+        self.m, self.n, self.k = m, n, k
+        self.out_dtype = out_dtype
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.row_blocks = max(1, min(row_blocks, (m + 127) // 128))
+        rows = -(-m // self.row_blocks)
+        self.block_rows = -(-rows // 128) * 128  # whole 128-row tiles per block
+        self.depth = depth
+        self._slot = 0
+        self._in, self._compute, self._out = (torch.cuda.Stream(self.device) for _ in range(3))
+        self._x = [torch.empty(m, k, dtype=torch.uint8, device=self.device) for _ in range(depth)]
+        self._y = [torch.empty(n, k, dtype=torch.uint8, device=self.device) for _ in range(depth)]
+        self._o = [torch.empty(m, n, dtype=out_dtype, device=self.device) for _ in range(depth)]
+        self._done: List[Optional[torch.cuda.Event]] = [None] * depth
+
+    def submit(self, x_host: torch.Tensor, y_host: torch.Tensor, out_host: torch.Tensor) -> torch.cuda.Event:
+        """Enqueue one GEMM; returns the event that fires when ``out_host`` is complete."""
+        m, n, k = self.m, self.n, self.k
+        if tuple(x_host.shape) != (m, k) or tuple(y_host.shape) != (n, k) or tuple(out_host.shape) != (m, n):
+            raise ValueError(f"expected x [{m},{k}], y stored as [{n},{k}], out [{m},{n}]")
+        if out_host.dtype != self.out_dtype:
+            raise TypeError(f"out_host must be {self.out_dtype}")
+        xh, yh = x_host.view(torch.uint8), y_host.view(torch.uint8)
+        slot = self._slot
+        self._slot = (slot + 1) % self.depth
+        xd, yd, od = self._x[slot], self._y[slot], self._o[slot]
+        caller = torch.cuda.current_stream(self.device)
+        self._in.wait_stream(caller)  # the host buffers may have been produced by work on the caller's stream
+        if self._done[slot] is not None:
+            self._in.wait_event(self._done[slot])  # this slot's previous download must have left the device buffers
+        blocks = [(r, min(r + self.block_rows, m)) for r in range(0, m, self.block_rows)]
+        arrived = []
+        with torch.cuda.stream(self._in):
+            yd.copy_(yh, non_blocking=True)
+            for r0, r1 in blocks:
+                xd[r0:r1].copy_(xh[r0:r1], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self._in)
+                arrived.append(ev)
+        y_op = yd.view(torch.float8_e4m3fn).t()
+        computed = []
+        with torch.cuda.stream(self._compute):
+            for (r0, r1), ev in zip(blocks, arrived):
+                self._compute.wait_event(ev)
+                ops.fp8_gemm(xd[r0:r1].view(torch.float8_e4m3fn), y_op, out_dtype=self.out_dtype, out=od[r0:r1])
+                ev2 = torch.cuda.Event()
+                ev2.record(self._compute)
+                computed.append(ev2)
+        with torch.cuda.stream(self._out):
+            for (r0, r1), ev in zip(blocks, computed):
+                self._out.wait_event(ev)
+                out_host[r0:r1].copy_(od[r0:r1], non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(self._out)
+        self._done[slot] = done
+        return done
+
+    def __call__(self, x_host: torch.Tensor, y_host: torch.Tensor, out_host: torch.Tensor) -> torch.Tensor:
+        """Blocking form: returns ``out_host`` once it is complete."""
+        self.submit(x_host, y_host, out_host).synchronize()
+        return out_host
+
+    def synchronize(self) -> None:
+        for ev in self._done:
+            if ev is not None:
+                ev.synchronize()

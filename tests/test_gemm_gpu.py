@@ -188,6 +188,25 @@ def test_output_scales(hb, m, n, k, config):
         hb.fp8_gemm(xd, yd, scale_a=one.half(), scale_b=one)
 
 
+def test_host_buffer_pipeline_equals_the_direct_call(hb):
+    """HostGemm (pinned operands in, pinned result out, row blocks on three streams, double-buffered
+    device copies) must give exactly what one fp8_gemm call on the whole matrix gives."""
+    m, n, k = 1100, 784, 640
+    x, y = o.gemm_inputs(m, n, k, seed=41)
+    x_pin = x.view(torch.uint8).pin_memory()
+    y_pin = y.t().contiguous().view(torch.uint8).pin_memory()  # [N, K] bytes = column-major y
+    want = hb.fp8_gemm(to_dev(x), to_dev(y), out_dtype=torch.bfloat16).cpu()
+    pipe = hb.HostGemm(m, n, k, out_dtype=torch.bfloat16, row_blocks=4)
+    outs = [torch.empty(m, n, dtype=torch.bfloat16).pin_memory() for _ in range(5)]
+    events = [pipe.submit(x_pin, y_pin, out) for out in outs]  # more calls in flight than buffer copies
+    for ev, out in zip(events, outs):
+        ev.synchronize()
+        assert torch.equal(out, want)
+    assert torch.equal(pipe(x_pin, y_pin, outs[0]), want)
+    with pytest.raises(ValueError, match="expected x"):
+        pipe.submit(x_pin[:8], y_pin, outs[0])
+
+
 def test_split_k_needs_its_workspace(hb):
     from helion_b200 import _lib
 
