@@ -39,12 +39,6 @@ enum WaitSite : uint32_t {
   SITE_ATTN_P_FULL = 16,
   SITE_ATTN_PV_DONE = 17,
   SITE_ATTN_O_FULL = 18,
-  SITE_ATTN_TILE_DONE = 19,
-  SITE_ATTN_XCHG = 20,
-  SITE_ATTN_XU_LOCK = 23,
-  SITE_ATTN_ALPHA = 21,
-  SITE_ATTN_O_READY = 22,
-  SITE_SPLITK = 30,
   SITE_SELFTEST = 40,
 };
 
@@ -56,18 +50,6 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
-}
-
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "elect.sync _|p, 0xffffffff;\n"
-      "selp.b32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(pred));
-  return pred != 0;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -109,21 +91,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Same, with cluster-scope acquire: used where the arrival comes from the peer CTA of a pair.
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-      "selp.b32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
 // Shared state of the bounded-wait scheme, one per CTA.
 struct WaitCtx {
   volatile uint32_t* abort_flag;  // shared memory, set by the first wait that runs out
@@ -150,27 +117,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   uint32_t spins = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (((++spins) & 0xffu) == 0u) {
-      if (*ctx.abort_flag) return false;
-      const unsigned long long now = global_timer_ns();
-      if (t0 == 0ull) {
-        t0 = now;
-      } else if (now - t0 > HB_WAIT_LIMIT_NS) {
-        record_timeout(ctx, site);
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, uint32_t site) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  // The global timer is slow to read, so the clock of the limit only starts at the first check
-  // (256 failed polls in); a wait that is satisfied quickly never touches it.
-  unsigned long long t0 = 0ull;
-  uint32_t spins = 0;
-  for (;;) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
     if (((++spins) & 0xffu) == 0u) {
       if (*ctx.abort_flag) return false;
       const unsigned long long now = global_timer_ns();
@@ -317,19 +263,6 @@ __device__ __forceinline__ void umma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uin
       : "memory");
 }
 
-// D[tmem] (+)= A[tmem] * B[smem].
-__device__ __forceinline__ void umma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                           uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 // Arrive on an mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -401,10 +334,6 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 // arrive on an mbarrier given by its shared::cluster address (own or peer CTA)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // TMA load into this CTA's shared memory whose completion bytes are counted on an mbarrier that

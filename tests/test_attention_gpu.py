@@ -172,6 +172,19 @@ def test_balanced_tile_order_is_bit_identical(hb, batch, heads, seq, dim, config
     _lib.check_status(0)
 
 
+def test_default_row_for_long_sequences_at_head_dim_64(hb):
+    """cfg_id = -1 takes the 64-key-step row from 2048 keys up at head_dim 64 (faster there) and row 0
+    otherwise; both are exact-running-max rows, so the default stays inside the stated tolerance of
+    the single-tile result and equals the explicitly chosen row bit for bit."""
+    (q8, k8, v8), (qd, kd, vd) = make_inputs(1, 2, 2048, 64, seed=17, v_contiguous=False)
+    auto = hb.fp8_attention(qd, kd, vd, 1, 2, out_dtype=torch.float32)
+    assert torch.equal(auto, hb.fp8_attention(qd, kd, vd, 1, 2, out_dtype=torch.float32, config=4))
+    _, one_raw = o.fp8_attention(bits(q8), bits(k8), bits(v8), 1, 2, return_parts=True)
+    np.testing.assert_allclose(auto.cpu().numpy(), one_raw, rtol=2e-2, atol=2e-2)
+    (_, _, _), (qd, kd, vd) = make_inputs(1, 2, 1024, 64, seed=17, v_contiguous=False)
+    assert torch.equal(hb.fp8_attention(qd, kd, vd, 1, 2), hb.fp8_attention(qd, kd, vd, 1, 2, config=0))
+
+
 def test_balanced_entry_rejects_a_bad_workspace(hb, built_library):
     import ctypes
 
