@@ -348,6 +348,11 @@ def main() -> None:
     e2e_value = world * GEMM_FLOPS / (float(e2e_ms.item()) * 1e-3) / 1e12
     got = out_pin[:64].float().numpy()
 
+    # ---- strong scaling of the two sharded BASELINE configurations (all ranks take part) -------
+    strong = None
+    if world > 1 and not args.no_extras:
+        strong = strong_scaling_section(hb, torch, dist, dev, rank, world, flush)
+
     line = None
     if rank == 0:
         # sanity of the e2e result against the oracle on a row block (not timed)
@@ -418,11 +423,49 @@ def main() -> None:
                 "aten_scaled_mm_cpu_gflops_256": aten_scaled_mm_cpu_gflops(),
             }
         line.update(extras)
+        if strong is not None:
+            line["strong_scaling"] = strong
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
         emit(line)
+
+
+def strong_scaling_section(hb, torch, dist, dev, rank, world, flush) -> dict:
+    """Fixed global problems split over the ranks with no collective: the 8192^3 GEMM by row blocks of x
+    (y replicated) and attention B8 H32 S4096 D128 by batch*head slices.  Time = max over ranks of the
+    median launch time of the rank's shard; value = global FLOPs / that time."""
+    from helion_b200.sharding import shard_range
+
+    res = {}
+
+    def shard_time(fn):
+        ts = time_steps(fn, 10, 3, flush, torch)
+        t = torch.tensor([statistics.median(ts)], dtype=torch.float64, device=dev)
+        dist.barrier()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    g = torch.Generator(device=dev).manual_seed(1)
+    r0, r1 = shard_range(M, world, rank)
+    xs = torch.randn(r1 - r0, K, device=dev, generator=g).to(torch.float8_e4m3fn)
+    ys = torch.randn(N, K, device=dev, generator=g).to(torch.float8_e4m3fn).t()
+    outs = torch.empty(r1 - r0, N, dtype=torch.bfloat16, device=dev)
+    ms = shard_time(lambda: hb.fp8_gemm(xs, ys, out_dtype=torch.bfloat16, out=outs))
+    res["gemm_8192_row_sharded"] = {"ms": ms, "tflops": GEMM_FLOPS / (ms * 1e-3) / 1e12, "rows_per_rank": r1 - r0}
+
+    b, h, s, d = ATTN_SHAPES["attn_B8_H32_S4096_D128"]
+    b0, b1 = shard_range(b * h, world, rank)
+    nbh = b1 - b0
+    q = torch.randn(nbh, s, d, device=dev, generator=g).to(torch.float8_e4m3fn)
+    k = torch.randn(nbh, s, d, device=dev, generator=g).to(torch.float8_e4m3fn)
+    v = torch.randn(nbh, s, d, device=dev, generator=g).to(torch.float8_e4m3fn).permute(0, 2, 1)
+    outa = torch.empty(nbh, s, d, dtype=torch.float8_e4m3fn, device=dev)
+    ms = shard_time(lambda: hb.attention_into(q, k, v, outa))
+    res["attn_B8_H32_S4096_D128_bh_sharded"] = {"ms": ms, "tflops": 4.0 * b * h * s * s * d / (ms * 1e-3) / 1e12,
+                                                "slices_per_rank": nbh}
+    return res
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch, from the committed ncu summary
