@@ -521,6 +521,14 @@ def make_workload(name: str, torch, dev, hb, config=None):
         outg = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         return (lambda: hb.fp8_gemm(xa, ya, out_dtype=torch.bfloat16, out=outg, config=config, scale_a=sa, scale_b=sb),
                 GEMM_FLOPS, M * K + K * N + 2 * M * N + 4 * (M + N))
+    if name == "matmul_bf16_8192":  # hb200_gemm_16bit: the reference's examples/matmul.py shape class, row-major y
+        g = torch.Generator(device=dev).manual_seed(5)
+        xa = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        ya = torch.randn(K, N, device=dev, generator=g).to(torch.bfloat16)
+        bias = torch.randn(N, device=dev, generator=g).to(torch.bfloat16)
+        outg = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        return (lambda: hb.matmul(xa, ya, bias=bias, relu=True, out=outg, config=config),
+                GEMM_FLOPS, 2 * (M * K + K * N + M * N) + 2 * N)
     if name.startswith("preprocess_"):  # q, k, v fp16 -> e4m3 in one launch (hb200_fp8_attention_preprocess)
         b, h, s, d = ATTN_SHAPES["attn_" + name[len("preprocess_"):]]
         g = torch.Generator(device=dev).manual_seed(4)
@@ -531,7 +539,7 @@ def make_workload(name: str, torch, dev, hb, config=None):
 
 PREPROCESS = [f"preprocess_{n[len('attn_'):]}" for n in ATTN_SHAPES]
 WORKLOADS = ["gemm_8192", *ATTN_SHAPES, *(f"mlp_M{m}" for m in MLP_M), "cublaslt_8192", "gemm_8192_rowwise_scaled",
-             *PREPROCESS]
+             "matmul_bf16_8192", *PREPROCESS]
 
 
 def run_only(args, torch, dev, hb, _lib, emit) -> None:
@@ -566,6 +574,10 @@ def run_extras(hb, _lib, o, torch, dev, flush, fp8_peak, peaks) -> dict:
     res["mlp_K4096_N14336"] = {f"M{m}": entry(f"mlp_M{m}") for m in MLP_M}
     # the callers either side of the two kernels: scaled GEMM epilogue, attention input preparation
     res["gemm_8192_rowwise_scaled"] = entry("gemm_8192_rowwise_scaled")
+    e = entry("matmul_bf16_8192")  # bf16 operands: fractions are of the measured / nominal bf16 peak, not FP8
+    res["matmul_bf16_8192_bias_relu"] = {"ms": e["ms"], "ms_min": e["ms_min"], "tflops": e["tflops"],
+                                         "frac_of_measured_bf16_peak": e["tflops"] / peaks["bf16_tflops"],
+                                         "frac_of_nominal_2250": e["tflops"] / 2250.0}
     res["attention_preprocess_fp16"] = {}
     for name in PREPROCESS:
         e = entry(name)

@@ -4,6 +4,7 @@ Public surface:
     fp8_gemm, fp8_attention         -- operators on torch CUDA tensors (helion_b200.ops)
     preprocess_fp8_attention_inputs -- q, k, v -> e4m3 in one kernel, with the reference's views
     HostGemm                        -- fp8_gemm on pinned host buffers with overlapped PCIe copies
+    matmul                          -- fp16 / bf16 sibling of fp8_gemm with the bias / ReLU epilogues
     DropInKernel                    -- object with the protocol of helion.runtime.kernel.Kernel
                                        that the reference's test and benchmark harness touch
 There is no CPU, Triton or PyTorch fallback: calls fail loudly when the CUDA library is missing.
@@ -12,7 +13,7 @@ from __future__ import annotations
 
 from ._lib import DeviceWaitTimeout, LibraryNotBuiltError
 from .host_io import HostGemm
-from .ops import attention_into, fp8_attention, fp8_gemm, preprocess_fp8_attention_inputs
+from .ops import attention_into, fp8_attention, fp8_gemm, matmul, preprocess_fp8_attention_inputs
 
 __all__ = [
     "fp8_gemm",
@@ -20,6 +21,7 @@ __all__ = [
     "attention_into",
     "preprocess_fp8_attention_inputs",
     "HostGemm",
+    "matmul",
     "DeviceWaitTimeout",
     "LibraryNotBuiltError",
 ]

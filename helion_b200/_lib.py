@@ -45,6 +45,11 @@ SIGNATURES = {
         [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.c_int, _vp, _vp, ctypes.c_int,
          ctypes.c_int, _vp, ctypes.c_size_t, ctypes.c_int, _vp],
     ),
+    "hb200_gemm_16bit": (
+        ctypes.c_int,
+        [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.c_int, ctypes.c_int, _vp, ctypes.c_int,
+         ctypes.c_int, ctypes.c_int, _vp],
+    ),
     "hb200_fp8_gemm_splitk_static": (
         ctypes.c_int,
         [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp],

@@ -323,6 +323,73 @@ int hb200_fp8_gemm_scaled(const void* x, const void* y, void* out, int64_t M, in
                        cfg_id, workspace, workspace_bytes, device, stream);
 }
 
+int hb200_gemm_16bit(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K, int64_t x_rs, int64_t x_cs,
+                     int64_t y_rs, int64_t y_cs, int64_t out_rs, int in_dtype, int out_dtype, const float* bias, int relu,
+                     int cfg_id, int device, void* stream) {
+  if (in_dtype != HB200_DT_FP16 && in_dtype != HB200_DT_BF16) {
+    return set_error(HB200_ERR_BAD_DTYPE, "gemm_16bit: in_dtype must be FP16 or BF16");
+  }
+  if (out_dtype != in_dtype && out_dtype != HB200_DT_FP32) {
+    return set_error(HB200_ERR_BAD_DTYPE, "gemm_16bit: out_dtype must be the operands' dtype or FP32");
+  }
+  if (M < 1 || N < 1 || K < 1 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX / 2) {
+    return set_error(HB200_ERR_BAD_SHAPE, "gemm_16bit: M, N must be in [1, 2^31) and K in [1, 2^30)");
+  }
+  if (K % 8 != 0) return set_error(HB200_ERR_BAD_SHAPE, "gemm_16bit: K must be a multiple of 8");
+  if (N % 8 != 0) return set_error(HB200_ERR_BAD_SHAPE, "gemm_16bit: N must be a multiple of 8");
+  if (x == nullptr || y == nullptr || out == nullptr) return set_error(HB200_ERR_ALIGN, "gemm_16bit: null pointer");
+  if (x_cs != 1) return set_error(HB200_ERR_BAD_STRIDE, "gemm_16bit: x must be row-major (column stride 1)");
+  if (x_rs < K || x_rs % 8 != 0) {
+    return set_error(HB200_ERR_BAD_STRIDE, "gemm_16bit: x row stride must be >= K and a multiple of 8");
+  }
+  bool y_colmajor;
+  int64_t ldb;
+  if (y_rs == 1 && (K == 1 || y_cs >= K)) {
+    y_colmajor = true;
+    ldb = y_cs;
+  } else if (y_cs == 1 && y_rs >= N) {
+    y_colmajor = false;
+    ldb = y_rs;
+  } else {
+    return set_error(HB200_ERR_BAD_STRIDE, "gemm_16bit: y must be column-major (row stride 1) or row-major (column stride 1)");
+  }
+  if (ldb % 8 != 0) return set_error(HB200_ERR_BAD_STRIDE, "gemm_16bit: y leading stride must be a multiple of 8");
+  const int64_t out_elem = out_dtype == HB200_DT_FP32 ? 4 : 2;
+  if (out_rs < N || (out_rs * out_elem) % 16 != 0) {
+    return set_error(HB200_ERR_BAD_STRIDE, "gemm_16bit: out row stride must be >= N and give 16-byte aligned rows");
+  }
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out)) & 15u) {
+    return set_error(HB200_ERR_ALIGN, "gemm_16bit: x, y and out must be 16-byte aligned");
+  }
+  if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 3u)) {
+    return set_error(HB200_ERR_ALIGN, "gemm_16bit: bias must be 4-byte aligned");
+  }
+  DeviceCtx* ctx = get_device_ctx(device);
+  if (ctx == nullptr) return ctx_error_code(device);
+  GemmArgs a;
+  a.x = x;
+  a.y = y;
+  a.out = out;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.lda = x_rs;
+  a.ldb = ldb;
+  a.y_colmajor = y_colmajor;
+  a.ldc = out_rs;
+  a.out_dtype = out_dtype;
+  a.cfg_id = cfg_id;
+  a.workspace = nullptr;
+  a.workspace_bytes = 0;
+  a.device = device;
+  a.stream = static_cast<cudaStream_t>(stream);
+  a.kind = in_dtype == HB200_DT_FP16 ? 1 : 2;
+  a.bias = bias;
+  a.relu = relu != 0 ? 1 : 0;
+  DeviceGuard guard(device);
+  return launch_gemm_16bit(a, ctx);
+}
+
 int hb200_fp8_gemm_splitk_static(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K,
                                  int64_t x_rs, int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs, int out_dtype,
                                  int splits, int device, void* stream) {

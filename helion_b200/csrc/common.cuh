@@ -25,6 +25,10 @@ namespace hb {
 constexpr unsigned long long HB_WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
 constexpr unsigned long long HB_DRAIN_LIMIT_NS = 200000000ull;  // 0.2 s per drain wait
 
+// Operand kinds of the GEMM kernels: e4m3 (kind::f8f6f4) or 16-bit floats (kind::f16).  All of them
+// move 32 bytes of K per instruction, so the byte-oriented pipelines are shared.
+enum OperandKind : int { KIND_E4M3 = 0, KIND_F16 = 1, KIND_BF16 = 2 };
+
 enum WaitSite : uint32_t {
   SITE_GEMM_EMPTY = 1,
   SITE_GEMM_FULL = 2,
@@ -263,6 +267,26 @@ __device__ __forceinline__ void umma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uin
       : "memory");
 }
 
+// Same for 16-bit operands (f16 or bf16 per the instruction descriptor), K = 16 elements.
+__device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <int KIND>
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  if constexpr (KIND == KIND_E4M3) umma_f8_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+  else umma_f16_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+}
+
 // Arrive on an mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -374,6 +398,25 @@ __device__ __forceinline__ void umma_f8_ss_pair(uint32_t d_tmem, uint64_t a_desc
       : "memory");
 }
 
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <int KIND>
+__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  if constexpr (KIND == KIND_E4M3) umma_f8_ss_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+  else umma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+}
+
 // Arrive (once) on the mbarrier at a shared::cluster address when all MMAs issued so far by this
 // thread have completed.  Used twice in a row to signal the same event to both CTAs of a pair.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
@@ -416,6 +459,15 @@ __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) 
 //   bit 15 A major (0 = K, 1 = MN)   bit 16 B major   bits [17,23) N >> 3   bits [24,29) M >> 4
 __host__ __device__ constexpr uint32_t make_idesc_e4m3(uint32_t m, uint32_t n, bool a_mn_major, bool b_mn_major) {
   return (1u << 4) | (0u << 7) | (0u << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+         ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// Instruction descriptor for any of the kinds above (fp32 accumulator).  kind::f16 encodes f16 as
+// format 0 and bf16 as format 1 in the same A / B format fields.
+template <int KIND>
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t m, uint32_t n, bool a_mn_major, bool b_mn_major) {
+  constexpr uint32_t fmt = KIND == KIND_BF16 ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
          ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 

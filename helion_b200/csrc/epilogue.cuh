@@ -9,14 +9,41 @@ namespace hb {
 // Optional output scaling of the GEMM epilogues: out = cast((acc * a) * b), the multiplications in
 // fp32 in that order.  mode 0: none.  mode 1: a and b point to one float each (per-tensor scales).
 // mode 2: a has one float per row of out, b one per column (row-wise scales).
+// Then, optionally, `+ bias[column]` (fp32, one per column of out) and `max(., 0)`: the two epilogues
+// of the reference's matmul example (examples/matmul.py:96-117, `acc + bias[tile[1]]` and
+// `relu(acc + bias[tile[1]])`).
 struct EpiScale {
   const float* a;
   const float* b;
   int mode;
+  const float* bias;
+  int relu;
 };
 
 // Scales 32 consecutive columns [col0, col0 + 32) of one output row held as fp32 bit patterns.
+__device__ __forceinline__ void bias_relu_chunk(uint32_t (&r)[32], const EpiScale& sc, int col0, int N) {
+  if (sc.bias != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float b = col0 + i < N ? __ldg(sc.bias + col0 + i) : 0.0f;
+      r[i] = __float_as_uint(__uint_as_float(r[i]) + b);
+    }
+  }
+  if (sc.relu) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(fmaxf(__uint_as_float(r[i]), 0.0f));
+  }
+}
+
 __device__ __forceinline__ void scale_chunk(uint32_t (&r)[32], const EpiScale& sc, int row, int M, int col0, int N) {
+  if (sc.bias != nullptr || sc.relu) {
+    EpiScale only_scales = sc;
+    only_scales.bias = nullptr;
+    only_scales.relu = 0;
+    scale_chunk(r, only_scales, row, M, col0, N);
+    bias_relu_chunk(r, sc, col0, N);
+    return;
+  }
   if (sc.mode == 0) return;
   if (sc.mode == 1) {
     const float sa = __ldg(sc.a), sb = __ldg(sc.b);
@@ -45,6 +72,6 @@ __device__ __forceinline__ void scale_chunk(uint32_t (&r)[32], const EpiScale& s
   }
 }
 
-inline EpiScale epi_scale(const GemmArgs& a) { return EpiScale{a.scale_a, a.scale_b, a.scale_mode}; }
+inline EpiScale epi_scale(const GemmArgs& a) { return EpiScale{a.scale_a, a.scale_b, a.scale_mode, a.bias, a.relu}; }
 
 }  // namespace hb

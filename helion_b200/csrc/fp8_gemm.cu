@@ -28,8 +28,12 @@ namespace hb {
 namespace {
 
 constexpr int BM = 128;      // rows of one output tile = UMMA M
-constexpr int BK = 128;      // bytes (= e4m3 elements) of K per pipeline stage = one swizzle row
-constexpr int UMMA_K = 32;   // K of one kind::f8f6f4 instruction
+constexpr int BK = 128;      // BYTES of K per pipeline stage = one swizzle row (128 e4m3 or 64 16-bit elements)
+constexpr int UMMA_K = 32;   // bytes of K per instruction (32 e4m3 elements for kind::f8f6f4, 16 for kind::f16)
+// The kernels are written over bytes: K arrives as the byte length of a row of x, and operands with
+// K contiguous look the same for every element size.  Only an operand with N contiguous ("MN-major":
+// a row-major y) depends on the element size ES: a stage then holds BK/ES rows of K, and a 128-byte
+// swizzle row spans 128/ES columns.
 constexpr int NUM_THREADS = 192;
 constexpr int NUM_EPI_THREADS = 128;
 
@@ -147,7 +151,7 @@ struct StagedStore {
   }
 };
 
-template <int BN, int STAGES, bool B_MN_MAJOR, int OUT_DT>
+template <int BN, int STAGES, bool B_MN_MAJOR, int OUT_DT, int KIND = KIND_E4M3>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, void* out,
                 int M, int N, int K, int64_t ldc, int group_m, uint32_t* status, int splits, float* partials,
@@ -155,6 +159,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   // splits > 1: split-K.  Work unit u = (tile u % num_tiles, K range u / num_tiles); every unit writes
   // its fp32 partial tile to partials[split][M][N] and splitk_reduce_kernel sums and converts.
   using L = GemmLayout<BN, STAGES>;
+  constexpr int ES = KIND == KIND_E4M3 ? 1 : 2;  // element size of x and y
+  constexpr int KROWS = BK / ES;                 // K rows of an MN-major B stage
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
@@ -226,10 +232,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             // y column-major: rows of the map are columns of y, K is contiguous.
             tma_load_2d(b_dst, &tmap_b, &full[s], kb * BK, tc.n_blk * BN);
           } else {
-            // y row-major: N is contiguous; one box = 128 K rows x 128 bytes of N.
+            // y row-major: N is contiguous; one box = BK/ES K rows x 128 bytes of N (coordinates in bytes / rows).
 #pragma unroll
-            for (int j = 0; j < BN / 128; ++j) {
-              tma_load_2d(b_dst + j * (BK * 128), &tmap_b, &full[s], tc.n_blk * BN + j * 128, kb * BK);
+            for (int j = 0; j < BN * ES / 128; ++j) {
+              tma_load_2d(b_dst + j * (KROWS * 128), &tmap_b, &full[s], tc.n_blk * BN * ES + j * 128, kb * KROWS);
             }
           }
         }
@@ -244,7 +250,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ----------------------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_e4m3(BM, BN, false, B_MN_MAJOR);
+      constexpr uint32_t idesc = make_idesc<KIND>(BM, BN, false, B_MN_MAJOR);
       uint32_t it = 0;
       uint32_t tile_iter = 0;
       bool ok = true;
@@ -272,14 +278,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           // A: K-major, 128-byte rows, 8-row atoms 1024 B apart.
           const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024, SWZ_128B);
           // B K-major: same shape of atom.  B MN-major: 128 bytes of N contiguous, 8 K rows per
-          // atom (1024 B apart), consecutive 128-column blocks BK*128 bytes apart.
-          const uint64_t b_desc = B_MN_MAJOR ? make_smem_desc(b_addr, BK * 128, 1024, SWZ_128B)
+          // atom (1024 B apart), consecutive 128-byte column blocks KROWS*128 bytes apart; one
+          // instruction consumes UMMA_K/ES rows of K.
+          const uint64_t b_desc = B_MN_MAJOR ? make_smem_desc(b_addr, KROWS * 128, 1024, SWZ_128B)
                                              : make_smem_desc(b_addr, 16, 1024, SWZ_128B);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t ad = desc_advance(a_desc, k * UMMA_K);
-            const uint64_t bd = desc_advance(b_desc, B_MN_MAJOR ? k * UMMA_K * 128 : k * UMMA_K);
-            umma_f8_ss(d_tmem, ad, bd, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
+            const uint64_t bd = desc_advance(b_desc, B_MN_MAJOR ? k * (UMMA_K / ES) * 128 : k * UMMA_K);
+            umma_ss<KIND>(d_tmem, ad, bd, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty[s]);  // smem stage is free once these MMAs have read it
         }
@@ -404,12 +411,14 @@ struct PairLayout {
 constexpr int PAIR_BM = 256;
 constexpr int PAIR_BN = 256;
 
-template <int STAGES, bool B_MN_MAJOR, int OUT_DT>
+template <int STAGES, bool B_MN_MAJOR, int OUT_DT, int KIND = KIND_E4M3>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_out, int M, int N, int K, int group_m, uint32_t* status,
                      EpiScale sc) {
   using L = PairLayout<STAGES>;
+  constexpr int ES = KIND == KIND_E4M3 ? 1 : 2;
+  constexpr int KROWS = BK / ES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
@@ -483,7 +492,11 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           if constexpr (!B_MN_MAJOR) {
             tma_load_2d_pair(b_dst, &tmap_b, full_leader, kb * BK, col0);
           } else {
-            tma_load_2d_pair(b_dst, &tmap_b, full_leader, col0, kb * BK);
+            // this CTA's 128 columns = ES blocks of 128 bytes x KROWS rows of K
+#pragma unroll
+            for (int j = 0; j < ES; ++j) {
+              tma_load_2d_pair(b_dst + j * (KROWS * 128), &tmap_b, full_leader, col0 * ES + j * 128, kb * KROWS);
+            }
           }
         }
       }
@@ -497,7 +510,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (leader CTA only) -----------------------------
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = make_idesc_e4m3(PAIR_BM, PAIR_BN, false, B_MN_MAJOR);
+      constexpr uint32_t idesc = make_idesc<KIND>(PAIR_BM, PAIR_BN, false, B_MN_MAJOR);
       uint32_t it = 0;
       uint32_t tile_iter = 0;
       bool ok = true;
@@ -521,13 +534,13 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
           const uint32_t b_addr = a_addr + L::A_BYTES;
           const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024, SWZ_128B);
-          const uint64_t b_desc = B_MN_MAJOR ? make_smem_desc(b_addr, 1024, 1024, SWZ_128B)
+          const uint64_t b_desc = B_MN_MAJOR ? make_smem_desc(b_addr, KROWS * 128, 1024, SWZ_128B)
                                              : make_smem_desc(b_addr, 16, 1024, SWZ_128B);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t ad = desc_advance(a_desc, k * UMMA_K);
-            const uint64_t bd = desc_advance(b_desc, B_MN_MAJOR ? k * UMMA_K * 128 : k * UMMA_K);
-            umma_f8_ss_pair(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            const uint64_t bd = desc_advance(b_desc, B_MN_MAJOR ? k * (UMMA_K / ES) * 128 : k * UMMA_K);
+            umma_ss_pair<KIND>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           // the stage is free in BOTH CTAs once these MMAs have read it
           const uint32_t e_local = smem_u32(&empty[s]);
@@ -621,12 +634,14 @@ constexpr int PAIR2_BM = 512;
 constexpr int PAIR2_BN = 256;
 constexpr int PAIR2_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 
-template <int STAGES, bool B_MN_MAJOR, int OUT_DT>
+template <int STAGES, bool B_MN_MAJOR, int OUT_DT, int KIND = KIND_E4M3>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR2_THREADS, 1)
 fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_out, int M, int N, int K, int group_m,
                       uint32_t* status, EpiScale sc) {
   using L = Pair2Layout<STAGES>;
+  constexpr int ES = KIND == KIND_E4M3 ? 1 : 2;
+  constexpr int KROWS = BK / ES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
@@ -699,7 +714,10 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if constexpr (!B_MN_MAJOR) {
             tma_load_2d_pair(b_dst, &tmap_b, full_leader, kb * BK, col0);
           } else {
-            tma_load_2d_pair(b_dst, &tmap_b, full_leader, col0, kb * BK);
+#pragma unroll
+            for (int j = 0; j < ES; ++j) {
+              tma_load_2d_pair(b_dst + j * (KROWS * 128), &tmap_b, full_leader, col0 * ES + j * 128, kb * KROWS);
+            }
           }
         }
       }
@@ -712,7 +730,7 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (leader CTA only) -----------------------------
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = make_idesc_e4m3(256, PAIR2_BN, false, B_MN_MAJOR);
+      constexpr uint32_t idesc = make_idesc<KIND>(256, PAIR2_BN, false, B_MN_MAJOR);
       uint32_t it = 0;
       uint32_t tile_iter = 0;
       bool ok = true;
@@ -728,7 +746,7 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
           const uint32_t b_addr = a_addr + L::A_BYTES;
-          const uint64_t b_desc = B_MN_MAJOR ? make_smem_desc(b_addr, 1024, 1024, SWZ_128B)
+          const uint64_t b_desc = B_MN_MAJOR ? make_smem_desc(b_addr, KROWS * 128, 1024, SWZ_128B)
                                              : make_smem_desc(b_addr, 16, 1024, SWZ_128B);
           // accumulator by accumulator, so that in the first K block of a tile the MMAs into
           // accumulator 0 can start while the epilogue still drains accumulator 1
@@ -745,8 +763,8 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
               const uint64_t ad = desc_advance(a_desc, k * UMMA_K);
-              const uint64_t bd = desc_advance(b_desc, B_MN_MAJOR ? k * UMMA_K * 128 : k * UMMA_K);
-              umma_f8_ss_pair(tmem_base + acc * PAIR2_BN, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+              const uint64_t bd = desc_advance(b_desc, B_MN_MAJOR ? k * (UMMA_K / ES) * 128 : k * UMMA_K);
+              umma_ss_pair<KIND>(tmem_base + acc * PAIR2_BN, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
             }
           }
           if (!ok) break;
@@ -860,10 +878,16 @@ int encode_out_map(CUtensorMap* tout, const GemmArgs& a) {
                      box, out32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
-template <int STAGES, bool B_MN, int OUT_DT>
+// K as the kernels see it: the byte length of a row of x.
+template <int KIND>
+int k_bytes(const GemmArgs& a) {
+  return static_cast<int>(a.K * (KIND == KIND_E4M3 ? 1 : 2));
+}
+
+template <int STAGES, bool B_MN, int OUT_DT, int KIND = KIND_E4M3>
 int launch_pair_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
   using L = PairLayout<STAGES>;
-  auto kernel = fp8_gemm_pair_kernel<STAGES, B_MN, OUT_DT>;
+  auto kernel = fp8_gemm_pair_kernel<STAGES, B_MN, OUT_DT, KIND>;
   static bool attr_set[64] = {};
   if (!attr_set[a.device]) {
     HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
@@ -879,16 +903,16 @@ int launch_pair_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& t
     if (rc != HB200_OK) return rc;
   }
   kernel<<<2 * pairs, NUM_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, tout, static_cast<int>(a.M),
-                                                              static_cast<int>(a.N), static_cast<int>(a.K), group_m,
+                                                              static_cast<int>(a.N), k_bytes<KIND>(a), group_m,
                                                               ctx->status_dev, epi_scale(a));
   HB_CUDA_CHECK(cudaGetLastError());
   return HB200_OK;
 }
 
-template <bool B_MN, int OUT_DT>
+template <bool B_MN, int OUT_DT, int KIND = KIND_E4M3>
 int launch_pair2_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
   using L = Pair2Layout<4>;
-  auto kernel = fp8_gemm_pair2_kernel<4, B_MN, OUT_DT>;
+  auto kernel = fp8_gemm_pair2_kernel<4, B_MN, OUT_DT, KIND>;
   static bool attr_set[64] = {};
   if (!attr_set[a.device]) {
     HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
@@ -903,7 +927,7 @@ int launch_pair2_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& 
     if (rc != HB200_OK) return rc;
   }
   kernel<<<2 * pairs, PAIR2_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, tout, static_cast<int>(a.M),
-                                                                static_cast<int>(a.N), static_cast<int>(a.K), group_m,
+                                                                static_cast<int>(a.N), k_bytes<KIND>(a), group_m,
                                                                 ctx->status_dev, epi_scale(a));
   HB_CUDA_CHECK(cudaGetLastError());
   return HB200_OK;
@@ -945,11 +969,11 @@ static int effective_splits(int64_t K, int requested) {
   return (k_blocks + per - 1) / per;
 }
 
-template <int BN, int STAGES, bool B_MN, int OUT_DT>
+template <int BN, int STAGES, bool B_MN, int OUT_DT, int KIND = KIND_E4M3>
 int launch_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m,
                     int splits_requested = 1) {
   using L = GemmLayout<BN, STAGES>;
-  auto kernel = fp8_gemm_kernel<BN, STAGES, B_MN, OUT_DT>;
+  auto kernel = fp8_gemm_kernel<BN, STAGES, B_MN, OUT_DT, KIND>;
   static bool attr_set[64] = {};
   if (!attr_set[a.device]) {
     HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
@@ -958,7 +982,7 @@ int launch_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, co
   const int m_tiles = static_cast<int>((a.M + BM - 1) / BM);
   const int n_tiles = static_cast<int>((a.N + BN - 1) / BN);
   const int64_t num_tiles = static_cast<int64_t>(m_tiles) * n_tiles;
-  const int splits = effective_splits(a.K, splits_requested);
+  const int splits = effective_splits(k_bytes<KIND>(a), splits_requested);
   if (splits > 1) {
     const size_t need = static_cast<size_t>(splits) * a.M * a.N * sizeof(float);
     if (a.workspace == nullptr || a.workspace_bytes < need || (reinterpret_cast<uintptr_t>(a.workspace) & 15u)) {
@@ -968,7 +992,7 @@ int launch_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, co
   }
   const int grid = static_cast<int>(std::min<int64_t>(num_tiles * splits, ctx->num_sms));
   kernel<<<grid, NUM_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, a.out, static_cast<int>(a.M), static_cast<int>(a.N),
-                                                         static_cast<int>(a.K), a.ldc, group_m, ctx->status_dev, splits,
+                                                         k_bytes<KIND>(a), a.ldc, group_m, ctx->status_dev, splits,
                                                          static_cast<float*>(a.workspace), epi_scale(a));
   HB_CUDA_CHECK(cudaGetLastError());
   return splits > 1 ? launch_splitk_reduce(a, splits) : HB200_OK;
@@ -1255,6 +1279,81 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
     }
   }
   return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: config has no kernel instance");
+}
+
+// ------------------------------------------------------------------------------------------------
+// fp16 / bf16 operands through the same kernels (hb200_gemm_16bit).  The pipelines are byte-oriented, so
+// the tensor maps are built over bytes: a row of x is 2K bytes long, a 128-byte stage row is 64
+// elements of K, and the kernels get K as that byte length.
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+template <int KIND, int OUT_DT, bool B_MN>
+int launch16_row(const GemmArgs& a, DeviceCtx* ctx, const GemmConfig& c, const CUtensorMap& ta, const CUtensorMap& tb) {
+  if (c.skinny || c.splits > 1 || c.bn == 64) {
+    return set_error(HB200_ERR_BAD_CONFIG, "gemm_16bit: this table row exists for e4m3 operands only");
+  }
+  if (c.pair && c.bn == 512) return launch_pair2_instance<B_MN, OUT_DT, KIND>(a, ctx, ta, tb, c.group_m);
+  if (c.pair) return launch_pair_instance<6, B_MN, OUT_DT, KIND>(a, ctx, ta, tb, c.group_m);
+  if (c.bn == 256) return launch_instance<256, 4, B_MN, OUT_DT, KIND>(a, ctx, ta, tb, c.group_m);
+  return launch_instance<128, 6, B_MN, OUT_DT, KIND>(a, ctx, ta, tb, c.group_m);
+}
+
+template <int KIND, int OUT_DT>
+int launch16_layout(const GemmArgs& a, DeviceCtx* ctx, const GemmConfig& c, const CUtensorMap& ta, const CUtensorMap& tb) {
+  return a.y_colmajor ? launch16_row<KIND, OUT_DT, false>(a, ctx, c, ta, tb)
+                      : launch16_row<KIND, OUT_DT, true>(a, ctx, c, ta, tb);
+}
+
+}  // namespace
+
+int launch_gemm_16bit(const GemmArgs& a, DeviceCtx* ctx) {
+  constexpr int64_t ES = 2;
+  int cfg_id = a.cfg_id;
+  if (cfg_id < 0) {
+    cfg_id = gemm_select_config_nosplit(a.M, a.N, a.K * ES, a.y_colmajor, ctx->num_sms);
+    if (kGemmConfigs[cfg_id].bn == 64) cfg_id = 1;  // the 64-wide tile is not built for 16-bit operands
+    // Measured at 8192^3 (bf16 / fp16, either layout of y): the 256x256 pair tile runs 768-814 us, the
+    // 512x256 pair tile 786-998 us -- at half the tensor rate per byte of K its exposed epilogue no longer
+    // pays for the saved operand traffic.
+    if (kGemmConfigs[cfg_id].bn == 512) cfg_id = 6;
+  }
+  if (cfg_id >= kNumGemmConfigs) return set_error(HB200_ERR_BAD_CONFIG, "gemm_16bit: no such config");
+  const GemmConfig& c = kGemmConfigs[cfg_id];
+
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.K * ES), static_cast<uint64_t>(a.M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(a.lda * ES)};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(c.bn == 512 ? 256 : BM)};
+    int rc = encode_tmap_u8(&ta, a.x, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB200_OK) return rc;
+  }
+  if (a.y_colmajor) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.K * ES), static_cast<uint64_t>(a.N)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(a.ldb * ES)};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(c.pair ? 128 : c.bn)};
+    int rc = encode_tmap_u8(&tb, a.y, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB200_OK) return rc;
+  } else {
+    // row-major y: rows of the map are rows of K, 2N bytes long; a box is 64 K rows x 128 bytes (64 columns)
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.N * ES), static_cast<uint64_t>(a.K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(a.ldb * ES)};
+    const uint32_t box[2] = {128, static_cast<uint32_t>(BK / ES)};
+    int rc = encode_tmap_u8(&tb, a.y, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != HB200_OK) return rc;
+  }
+  if (a.kind == KIND_F16) {
+    if (a.out_dtype == HB200_DT_FP16) return launch16_layout<KIND_F16, HB200_DT_FP16>(a, ctx, c, ta, tb);
+    if (a.out_dtype == HB200_DT_FP32) return launch16_layout<KIND_F16, HB200_DT_FP32>(a, ctx, c, ta, tb);
+    return set_error(HB200_ERR_BAD_DTYPE, "gemm_16bit: fp16 operands give an FP16 or FP32 result");
+  }
+  if (a.kind == KIND_BF16) {
+    if (a.out_dtype == HB200_DT_BF16) return launch16_layout<KIND_BF16, HB200_DT_BF16>(a, ctx, c, ta, tb);
+    if (a.out_dtype == HB200_DT_FP32) return launch16_layout<KIND_BF16, HB200_DT_FP32>(a, ctx, c, ta, tb);
+    return set_error(HB200_ERR_BAD_DTYPE, "gemm_16bit: bf16 operands give a BF16 or FP32 result");
+  }
+  return set_error(HB200_ERR_BAD_DTYPE, "gemm_16bit: operands must be FP16 or BF16");
 }
 
 }  // namespace hb

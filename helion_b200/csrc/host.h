@@ -82,9 +82,15 @@ struct GemmArgs {
   const float* scale_a = nullptr;
   const float* scale_b = nullptr;
   int scale_mode = 0;
+  // 16-bit operands (hb200_gemm_16bit): 0 = e4m3, 1 = fp16, 2 = bf16; optional bias / ReLU epilogue
+  int kind = 0;
+  const float* bias = nullptr;
+  int relu = 0;
 };
 
 int launch_fp8_gemm(const GemmArgs& args, DeviceCtx* ctx);
+// Same kernels with fp16 / bf16 operands (args.kind); M, N, K and strides in elements.
+int launch_gemm_16bit(const GemmArgs& args, DeviceCtx* ctx);
 int gemm_num_configs();
 int gemm_describe_config(int cfg_id, char* buf, int buf_len);
 int gemm_select_config(int64_t M, int64_t N, int64_t K, bool y_colmajor, int out_dtype, int num_sms);

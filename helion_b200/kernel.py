@@ -139,7 +139,8 @@ class DropInKernel:
     # -- helion.Kernel protocol -----------------------------------------------------------------
     def bind(self, args: Sequence[Any]) -> BoundDropInKernel:
         key = tuple(
-            (a.dtype, a.device.type, tuple(a.shape), tuple(a.stride())) if isinstance(a, torch.Tensor) else a
+            (a.dtype, a.device.type, tuple(a.shape), tuple(a.stride())) if isinstance(a, torch.Tensor)
+            else getattr(a, "__code__", a)  # a closure argument (an epilogue) is keyed by its code, not its identity
             for a in args
         )  # the reference's static-shape specialisation key, helion/runtime/kernel.py:656-665
         bound = self._bound.get(key)

@@ -250,3 +250,61 @@ def preprocess_fp8_attention_inputs(
             )
             _lib.raise_for(code, "preprocess_fp8_attention_inputs")
     return q8.reshape(bh, seq, dim), k8.reshape(bh, seq, dim), v8.reshape(bh, seq, dim).permute(0, 2, 1)
+
+
+def matmul(
+    x: torch.Tensor,
+    y: torch.Tensor,
+    *,
+    bias: Optional[torch.Tensor] = None,
+    relu: bool = False,
+    out_dtype: Optional[torch.dtype] = None,
+    config: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """``out = epilogue(x @ y).to(out_dtype)`` for fp16 or bf16 ``x [M,K]``, ``y [K,N]``, fp32 accumulation.
+
+    The computation of the reference's ``matmul(x, y, epilogue)`` (examples/matmul.py:26-56) with the
+    epilogues its own checks use: identity, ``acc + bias[column]`` (``bias`` of N elements), and
+    ``relu(acc + bias[column])``.  The result has the operands' dtype (the reference's
+    ``promote_types``) unless ``out_dtype=torch.float32``.
+    """
+    if x.dtype != y.dtype or x.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(f"matmul expects two float16 or two bfloat16 operands, got {x.dtype} and {y.dtype}")
+    if x.dim() != 2 or y.dim() != 2:
+        raise ValueError(f"matmul expects 2-D inputs, got {tuple(x.shape)} and {tuple(y.shape)}")
+    m, k = x.shape
+    k2, n = y.shape
+    assert k == k2, f"size mismatch {k} != {k2}"  # same check and text as examples/matmul.py:47
+    out_dtype = x.dtype if out_dtype is None else out_dtype
+    if out_dtype not in (x.dtype, torch.float32):
+        raise TypeError(f"matmul out_dtype must be {x.dtype} or float32, got {out_dtype}")
+    dev = _require_cuda(x, y)
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    if y.stride(0) != 1 and y.stride(1) != 1:
+        y = y.contiguous()
+    bias32 = None
+    if bias is not None:
+        if bias.dim() != 1 or bias.shape[0] != n or bias.device != x.device:
+            raise ValueError(f"matmul: bias must be a vector of N={n} elements on the inputs' device")
+        bias32 = bias.to(torch.float32).contiguous()
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    elif out.dtype != out_dtype or tuple(out.shape) != (m, n) or out.stride(1) != 1 or out.device != x.device:
+        raise ValueError("matmul: `out` must be a row-major [M, N] tensor of out_dtype on the inputs' device")
+    if m == 0 or n == 0:
+        return out
+    if k == 0:
+        out.zero_()
+        if bias32 is not None:
+            out += bias32.to(out_dtype)
+        return out.relu_() if relu else out
+    code = _lib.load().hb200_gemm_16bit(
+        x.data_ptr(), y.data_ptr(), out.data_ptr(), m, n, k,
+        x.stride(0), x.stride(1), y.stride(0), y.stride(1), out.stride(0),
+        _OUT_DT[x.dtype], _OUT_DT[out_dtype], bias32.data_ptr() if bias32 is not None else None, int(bool(relu)),
+        -1 if config is None else int(config), dev, _stream_ptr(dev),
+    )
+    _lib.raise_for(code, "matmul")
+    return out

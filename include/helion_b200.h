@@ -91,6 +91,21 @@ HB200_API int hb200_fp8_gemm_scaled(const void* x, const void* y, void* out, int
                           const float* scale_a, const float* scale_b, int scale_mode, int cfg_id, void* workspace,
                           size_t workspace_bytes, int device, void* stream);
 
+/* out = cast(epilogue(x @ y)) for fp16 or bf16 x [M,K] and y [K,N] with fp32 accumulation: the same
+ * kernels with kind::f16 tensor-core instructions.  Replaces the device kernel of the reference's
+ * examples/matmul.py:26-56 (`matmul(x, y, epilogue)`; zero-initialised fp32 accumulator, torch.addmm
+ * per K tile, epilogue applied to the fp32 accumulator, cast to promote_types(x, y) on store).  The
+ * reference's epilogue is an arbitrary Python closure; here it is one of the three the reference's
+ * own checks use (examples/matmul.py:92-117): identity, `acc + bias[column]`, `relu(acc + bias[column])`.
+ *   in_dtype: HB200_DT_FP16 or HB200_DT_BF16 (both operands); out_dtype: the same, or HB200_DT_FP32.
+ *   x row-major; y row-major (what the reference passes) or column-major; strides in elements.
+ *   K % 8 == 0, N % 8 == 0, strides multiples of 8, pointers 16-byte aligned.
+ *   bias: NULL, or N floats (fp32; an fp16 / bf16 bias converts exactly); relu: 0 or 1.
+ *   cfg_id: a row of the GEMM table built for 16-bit operands (0, 1, 3-10, 14-17), or -1. */
+HB200_API int hb200_gemm_16bit(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K, int64_t x_rs,
+                     int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs, int in_dtype, int out_dtype,
+                     const float* bias, int relu, int cfg_id, int device, void* stream);
+
 /* Bytes of workspace hb200_fp8_gemm needs for this problem and configuration (0 for most). */
 HB200_API size_t hb200_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int cfg_id);
 

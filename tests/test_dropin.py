@@ -76,3 +76,27 @@ def test_calls_without_a_gpu_fail_loudly():
     x = torch.zeros(16, 16).to(torch.float8_e4m3fn)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         gemm_mod.fp8_gemm_tritonbench(x, x)
+
+
+def test_matmul_epilogue_recognition_needs_no_gpu():
+    """examples/matmul.py recognises the reference's three epilogues (examples/matmul.py:92-117) by
+    running the closure on a recording stand-in; everything else must raise instead of falling back."""
+    import torch
+
+    import examples.matmul as mod
+
+    bias = torch.arange(8, dtype=torch.float16)
+    assert mod._recognise(None, 8) == (None, False)
+    assert mod._recognise(lambda acc, tile: acc, 8) == (None, False)
+    b, relu = mod._recognise(lambda acc, tile: acc + bias[tile[1]], 8)
+    assert torch.equal(b, bias) and relu is False
+    b, relu = mod._recognise(lambda acc, tile: torch.relu(bias[tile[1]] + acc), 8)
+    assert torch.equal(b, bias) and relu is True
+    b, relu = mod._recognise(lambda acc, tile: torch.nn.functional.relu(acc), 8)
+    assert b is None and relu is True
+    for bad in (lambda acc, tile: acc * 2, lambda acc, tile: torch.tanh(acc), lambda acc, tile: torch.relu(acc) + bias,
+                lambda acc, tile: acc + bias.reshape(1, 8), lambda acc, tile: bias):
+        with pytest.raises(NotImplementedError):
+            mod._recognise(bad, 8)
+    with pytest.raises(ValueError, match="bias has"):
+        mod._recognise(lambda acc, tile: acc + bias[:4], 8)

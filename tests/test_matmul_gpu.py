@@ -1,0 +1,150 @@
+"""fp16 / bf16 matmul with the bias / ReLU epilogues on a B200: the kind::f16 instances of the GEMM
+kernels, called through the C ABI (helion_b200.ops.matmul -> hb200_gemm_16bit), against the CPU oracle
+(oracle.matmul_16bit, the restatement of the reference's examples/matmul.py).
+
+Gates: allclose(rtol=atol=2e-2) in every output dtype; relative Frobenius error against the fp32
+product of the exact operands <= 1e-3 for fp32 / fp16 results and <= 2.5e-3 for bf16 results (rounding
+an exact result to bf16 alone costs 1.7e-3); the fp32 result within 1e-5 of the largest output (order
+of the K sum only).  Every table row built for 16-bit operands must give the same fp32 result.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from helion_b200 import _lib
+from oracle import fp8_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+NAME = {torch.float16: "fp16", torch.bfloat16: "bf16", torch.float32: "fp32"}
+ROWS_16BIT = [0, 1, 3, 4, 5, 6, 7, 8, 9, 10, 14, 15, 16, 17]
+
+
+@pytest.fixture(scope="module")
+def hb(built_library):
+    import helion_b200
+
+    _lib.reset_status(0)
+    yield helion_b200
+    torch.cuda.synchronize()
+    _lib.check_status(0)
+
+
+def operands(m, n, k, dtype, seed, colmajor):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(m, k, generator=g).to(dtype)
+    y = torch.randn(n, k, generator=g).to(dtype).t() if colmajor else torch.randn(k, n, generator=g).to(dtype)
+    bias = torch.randn(n, generator=g).to(dtype)
+    yd = y.t().contiguous().cuda().t() if colmajor else y.cuda()
+    return (x, y, bias), (x.cuda(), yd, bias.cuda())
+
+
+def check(hb, host, dev, out_dtype, bias=False, relu=False, config=None):
+    (x, y, b), (xd, yd, bd) = host, dev
+    got = hb.matmul(xd, yd, bias=bd if bias else None, relu=relu, out_dtype=out_dtype, config=config)
+    assert got.dtype == out_dtype and tuple(got.shape) == (x.shape[0], y.shape[1])
+    got = got.float().cpu().numpy()
+    xf, yf = x.float().numpy(), y.float().numpy()
+    bf = b.float().numpy() if bias else None
+    want = o.matmul_16bit(xf, yf, bf, relu, NAME[out_dtype])
+    np.testing.assert_allclose(got, want, rtol=2e-2, atol=2e-2)
+    exact = o.matmul_16bit(xf, yf, bf, relu, "fp32")
+    assert o.rel_frobenius(got, exact) <= (2.5e-3 if out_dtype == torch.bfloat16 else 1e-3)
+    if out_dtype == torch.float32:
+        np.testing.assert_allclose(got, exact, rtol=1e-5, atol=1e-5 * float(np.abs(exact).max()))
+    return got
+
+
+@pytest.mark.parametrize("colmajor", [False, True], ids=["y_rowmajor", "y_colmajor"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (520, 784, 1152), (100, 272, 64), (1, 8, 8), (1000, 136, 72)])
+def test_matches_oracle(hb, m, n, k, dtype, colmajor):
+    host, dev = operands(m, n, k, dtype, seed=m + n + k, colmajor=colmajor)
+    for out_dtype in (dtype, torch.float32):
+        check(hb, host, dev, out_dtype)
+        check(hb, host, dev, out_dtype, bias=True)
+        check(hb, host, dev, out_dtype, bias=True, relu=True)
+    check(hb, host, dev, dtype, relu=True)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+def test_every_16bit_table_row_gives_the_same_result(hb, dtype):
+    for colmajor in (False, True):
+        host, dev = operands(520, 784, 1152, dtype, seed=5, colmajor=colmajor)
+        base = None
+        for cfg in ROWS_16BIT:
+            got = check(hb, host, dev, torch.float32, bias=True, relu=True, config=cfg)
+            base = got if base is None else base
+            np.testing.assert_allclose(got, base, rtol=1e-5, atol=1e-4)
+    for cfg in (2, 11, 18):  # 64-wide tile, split-K, operand-swapped rows are e4m3 only
+        with pytest.raises(ValueError, match="e4m3 operands only"):
+            hb.matmul(dev[0], dev[1], config=cfg)
+
+
+def test_example_module_and_epilogue_recognition(hb):
+    import examples.matmul as mod
+
+    mod.check(1024, 1024, 1024)  # the reference's own three comparisons against PyTorch
+    x = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
+    y = torch.randn(128, 192, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(192, device="cuda", dtype=torch.bfloat16)
+    want = torch.relu(x.float() @ y.float() + bias.float()).to(torch.bfloat16)
+    for epilogue in (lambda acc, tile: torch.relu(acc + bias[tile[1]]),
+                     lambda acc, tile: torch.nn.functional.relu(bias[tile[1]] + acc),
+                     lambda acc, tile: (acc + bias[tile[1]]).relu() if hasattr(acc, "relu") and callable(acc.relu) else None):
+        try:
+            got = mod.matmul(x, y, epilogue)
+        except (NotImplementedError, TypeError):
+            continue  # the third form is not a recognised spelling; it must fail loudly, not silently
+        torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    timed = mod.matmul_tritonbench(x, y, bias)
+    for _ in range(5):
+        a = timed()
+    torch.testing.assert_close(a.float(), (x.float() @ y.float() + bias.float()), rtol=2e-2, atol=2e-2)
+    assert len(mod.matmul._bound) <= 4  # a fresh closure per call must not grow the bind cache
+    with pytest.raises(NotImplementedError, match="built into the CUDA kernel"):
+        mod.matmul(x, y, lambda acc, tile: acc * 2.0)
+    with pytest.raises(NotImplementedError):
+        mod.matmul(x, y, lambda acc, tile: torch.sigmoid(acc))
+    with pytest.raises(ValueError, match="bias has"):
+        mod.matmul(x, y, lambda acc, tile: acc + bias[:100])
+
+
+def test_argument_checks(hb):
+    x = torch.zeros(64, 64, device="cuda", dtype=torch.float16)
+    with pytest.raises(TypeError, match="two float16 or two bfloat16"):
+        hb.matmul(x, x.bfloat16())
+    with pytest.raises(TypeError, match="out_dtype"):
+        hb.matmul(x, x, out_dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="multiple of 8"):
+        hb.matmul(x[:, :60].contiguous(), x[:60])
+    with pytest.raises(ValueError, match="bias must be a vector"):
+        hb.matmul(x, x, bias=torch.zeros(8, device="cuda"))
+
+
+class TestFullSize:
+    """8192^3 bf16: row blocks against the oracle plus exact properties."""
+
+    @pytest.fixture(scope="class")
+    def problem(self, hb):
+        g = torch.Generator(device="cuda").manual_seed(2)
+        x = torch.randn(8192, 8192, device="cuda", generator=g).to(torch.bfloat16)
+        y = torch.randn(8192, 8192, device="cuda", generator=g).to(torch.bfloat16)
+        return x, y
+
+    def test_row_blocks_match_oracle(self, hb, problem):
+        x, y = problem
+        out = hb.matmul(x, y, out_dtype=torch.float32)
+        yf = y.float().cpu().numpy()
+        for r in (0, 4097, 8064):
+            want = o.matmul_16bit(x[r:r + 128].float().cpu().numpy(), yf, None, False, "fp32")
+            np.testing.assert_allclose(out[r:r + 128].cpu().numpy(), want, rtol=1e-5, atol=1e-5 * float(np.abs(want).max()))
+
+    def test_row_permutation_and_doubling_commute_exactly(self, hb, problem):
+        x, y = problem
+        out = hb.matmul(x, y)
+        perm = torch.randperm(8192, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
+        assert torch.equal(hb.matmul(x[perm], y), out[perm])
+        assert torch.equal(hb.matmul(x * 2, y, out_dtype=torch.float32), hb.matmul(x, y, out_dtype=torch.float32) * 2)

@@ -124,3 +124,26 @@ def test_scaled_gemm_oracle_against_aten_and_its_own_identities():
     np.testing.assert_array_equal(o.fp8_gemm_scaled(xb, yb, ra, rb, "fp32"), (full * ra[:, None]) * rb[None, :])
     with pytest.raises(ValueError):
         o.fp8_gemm_scaled(xb, yb, ra, np.float32(1.0), "fp32")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+def test_matmul_16bit_oracle_against_torch(dtype):
+    """The reference's matmul example cannot run in ref-eager mode on a CPU (aten::mm.dtype is
+    CUDA-only), so its restatement is checked against torch's own fp32 matmul of the upcast operands
+    and torch's casts: same values up to the order of the fp32 K sum."""
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(72, 160, generator=g).to(dtype)
+    y = torch.randn(160, 136, generator=g).to(dtype)
+    bias = torch.randn(136, generator=g).to(dtype)
+    name = "fp16" if dtype == torch.float16 else "bf16"
+    acc = x.float() @ y.float()
+    for b, relu in ((None, False), (bias, False), (bias, True)):
+        want = acc if b is None else acc + b.float()
+        want = torch.relu(want) if relu else want
+        got = o.matmul_16bit(x.float().numpy(), y.float().numpy(), None if b is None else b.float().numpy(), relu, name)
+        got32 = o.matmul_16bit(x.float().numpy(), y.float().numpy(), None if b is None else b.float().numpy(), relu, "fp32")
+        np.testing.assert_allclose(got32, want.numpy(), rtol=1e-5, atol=1e-4)
+        # after the cast at most the last bit differs (where the fp32 values straddle a rounding boundary)
+        np.testing.assert_allclose(got, want.to(dtype).float().numpy(), rtol=2 ** -7 if name == "bf16" else 2 ** -10, atol=1e-3)
+    with pytest.raises(AssertionError, match="size mismatch"):
+        o.matmul_16bit(np.zeros((4, 8), np.float32), np.zeros((16, 4), np.float32))
