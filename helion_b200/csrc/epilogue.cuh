@@ -35,15 +35,7 @@ __device__ __forceinline__ void bias_relu_chunk(uint32_t (&r)[32], const EpiScal
   }
 }
 
-__device__ __forceinline__ void scale_chunk(uint32_t (&r)[32], const EpiScale& sc, int row, int M, int col0, int N) {
-  if (sc.bias != nullptr || sc.relu) {
-    EpiScale only_scales = sc;
-    only_scales.bias = nullptr;
-    only_scales.relu = 0;
-    scale_chunk(r, only_scales, row, M, col0, N);
-    bias_relu_chunk(r, sc, col0, N);
-    return;
-  }
+__device__ __forceinline__ void scales_only_chunk(uint32_t (&r)[32], const EpiScale& sc, int row, int M, int col0, int N) {
   if (sc.mode == 0) return;
   if (sc.mode == 1) {
     const float sa = __ldg(sc.a), sb = __ldg(sc.b);
@@ -70,6 +62,13 @@ __device__ __forceinline__ void scale_chunk(uint32_t (&r)[32], const EpiScale& s
       }
     }
   }
+}
+
+// The whole epilogue on one chunk: scales, then bias, then ReLU.  (Kept free of recursion and of copies
+// of `r`, so that the 32 values stay in registers.)
+__device__ __forceinline__ void scale_chunk(uint32_t (&r)[32], const EpiScale& sc, int row, int M, int col0, int N) {
+  scales_only_chunk(r, sc, row, M, col0, N);
+  bias_relu_chunk(r, sc, col0, N);
 }
 
 inline EpiScale epi_scale(const GemmArgs& a) { return EpiScale{a.scale_a, a.scale_b, a.scale_mode, a.bias, a.relu}; }
