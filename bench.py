@@ -494,15 +494,18 @@ def make_workload(name: str, torch, dev, hb, config=None):
         one = torch.tensor(1.0, device=dev)
         return (lambda: torch._scaled_mm(xa, ya, one, one, use_fast_accum=False, out_dtype=torch.bfloat16),
                 GEMM_FLOPS, M * K + K * N + 2 * M * N)
-    if name in ATTN_SHAPES:
-        b, h, s, d = ATTN_SHAPES[name]
+    if name in ATTN_SHAPES or name.startswith("attn_causal_"):
+        causal = name.startswith("attn_causal_")
+        b, h, s, d = ATTN_SHAPES["attn_" + name[len("attn_causal_"):]] if causal else ATTN_SHAPES[name]
         g = torch.Generator(device=dev).manual_seed(3)
         q = torch.randn(b * h, s, d, device=dev, generator=g).to(torch.float8_e4m3fn)
         k = torch.randn(b * h, s, d, device=dev, generator=g).to(torch.float8_e4m3fn)
         v = torch.randn(b * h, s, d, device=dev, generator=g).to(torch.float8_e4m3fn).permute(0, 2, 1)
         outa = torch.empty(b, h, s, d, dtype=torch.float8_e4m3fn, device=dev)
-        return (lambda: hb.fp8_attention(q, k, v, b, h, out=outa, config=config),
-                4.0 * b * h * s * s * d, 4 * b * h * s * d)
+        # with the mask a query row i multiplies against i + 1 keys: (S^2 + S) / 2 pairs instead of S^2
+        pairs = (s * s + s) / 2 if causal else s * s
+        return (lambda: hb.fp8_attention(q, k, v, b, h, out=outa, config=config, causal=causal),
+                4.0 * b * h * pairs * d, 4 * b * h * s * d)
     if name.startswith("mlp_M"):
         m = int(name[5:])
         g = torch.Generator(device=dev).manual_seed(2)
@@ -538,7 +541,8 @@ def make_workload(name: str, torch, dev, hb, config=None):
 
 
 PREPROCESS = [f"preprocess_{n[len('attn_'):]}" for n in ATTN_SHAPES]
-WORKLOADS = ["gemm_8192", *ATTN_SHAPES, *(f"mlp_M{m}" for m in MLP_M), "cublaslt_8192", "gemm_8192_rowwise_scaled",
+CAUSAL = [f"attn_causal_{n[len('attn_'):]}" for n in ATTN_SHAPES]
+WORKLOADS = ["gemm_8192", *ATTN_SHAPES, *CAUSAL, *(f"mlp_M{m}" for m in MLP_M), "cublaslt_8192", "gemm_8192_rowwise_scaled",
              "matmul_bf16_8192", *PREPROCESS]
 
 
@@ -571,6 +575,7 @@ def run_extras(hb, _lib, o, torch, dev, flush, fp8_peak, peaks) -> dict:
                 "frac_of_nominal_4500": tf / NOMINAL_FP8_TFLOPS, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
 
     res["attention"] = {name: entry(name) for name in ATTN_SHAPES}
+    res["attention_causal"] = {name: entry(name) for name in CAUSAL}  # FLOPs counted under the mask only
     res["mlp_K4096_N14336"] = {f"M{m}": entry(f"mlp_M{m}") for m in MLP_M}
     # the callers either side of the two kernels: scaled GEMM epilogue, attention input preparation
     res["gemm_8192_rowwise_scaled"] = entry("gemm_8192_rowwise_scaled")

@@ -457,8 +457,8 @@ int hb200_fp8_gemm_splitk_static(const void* x, const void* y, void* out, int64_
 
 // Validation and launch shared by the two attention entry points; workspace == nullptr selects
 // the static tile order.
-static int fp8_attention_impl(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S,
-                              int64_t D, const int64_t q_strides[3], const int64_t k_strides[3],
+static int fp8_attention_impl(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S, int64_t Sk,
+                              int causal, int64_t D, const int64_t q_strides[3], const int64_t k_strides[3],
                               const int64_t v_strides[3], const int64_t out_strides[3], float scale_log2,
                               int out_dtype, int cfg_id, void* workspace, size_t workspace_bytes, int device,
                               void* stream) {
@@ -469,7 +469,11 @@ static int fp8_attention_impl(const void* q, const void* k, const void* v, void*
   if (BH < 1 || S < 1 || BH > INT32_MAX || S > INT32_MAX) {
     return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: batch*heads and seq must be in [1, 2^31)");
   }
-  if (S % 16 != 0) return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: seq must be a multiple of 16");
+  if (S % 16 != 0 || Sk % 16 != 0) return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: seq must be a multiple of 16");
+  if (Sk < 1 || Sk > INT32_MAX) return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: seq_k must be in [1, 2^31)");
+  if (causal != 0 && Sk < S) {
+    return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: the causal mask needs seq_k >= seq_q (every query must see a key)");
+  }
   if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || q_strides == nullptr ||
       k_strides == nullptr || v_strides == nullptr || out_strides == nullptr) {
     return set_error(HB200_ERR_ALIGN, "fp8_attention: null pointer");
@@ -481,7 +485,7 @@ static int fp8_attention_impl(const void* q, const void* k, const void* v, void*
       q_strides[1] < D || k_strides[1] < D) {
     return set_error(HB200_ERR_BAD_STRIDE, "fp8_attention: q/k row and slice strides must be multiples of 16 and >= D");
   }
-  if (!((v_strides[1] == 1 && v_strides[2] >= D) || (v_strides[2] == 1 && v_strides[1] >= S))) {
+  if (!((v_strides[1] == 1 && v_strides[2] >= D) || (v_strides[2] == 1 && v_strides[1] >= Sk))) {
     return set_error(HB200_ERR_BAD_STRIDE,
                      "fp8_attention: v (logical [BH, D, S]) must have a unit stride along D or along S");
   }
@@ -505,6 +509,8 @@ static int fp8_attention_impl(const void* q, const void* k, const void* v, void*
   a.out = out;
   a.BH = BH;
   a.S = S;
+  a.Sk = Sk;
+  a.causal = causal != 0 ? 1 : 0;
   a.D = D;
   for (int i = 0; i < 3; ++i) {
     a.q_strides[i] = q_strides[i];
@@ -538,7 +544,7 @@ int hb200_fp8_attention(const void* q, const void* k, const void* v, void* out, 
                         const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
                         const int64_t out_strides[3], float scale_log2, int out_dtype, int cfg_id, int device,
                         void* stream) {
-  return fp8_attention_impl(q, k, v, out, BH, S, D, q_strides, k_strides, v_strides, out_strides, scale_log2,
+  return fp8_attention_impl(q, k, v, out, BH, S, S, 0, D, q_strides, k_strides, v_strides, out_strides, scale_log2,
                             out_dtype, cfg_id, nullptr, 0, device, stream);
 }
 
@@ -568,8 +574,16 @@ int hb200_fp8_attention_ws(const void* q, const void* k, const void* v, void* ou
                            const int64_t out_strides[3], float scale_log2, int out_dtype, int cfg_id, void* workspace,
                            size_t workspace_bytes, int device, void* stream) {
   if (workspace == nullptr) return set_error(HB200_ERR_WORKSPACE, "fp8_attention_ws: workspace is null");
-  return fp8_attention_impl(q, k, v, out, BH, S, D, q_strides, k_strides, v_strides, out_strides, scale_log2,
+  return fp8_attention_impl(q, k, v, out, BH, S, S, 0, D, q_strides, k_strides, v_strides, out_strides, scale_log2,
                             out_dtype, cfg_id, workspace, workspace_bytes, device, stream);
+}
+
+int hb200_fp8_attention_ex(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S_q, int64_t S_k,
+                           int64_t D, const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                           const int64_t out_strides[3], float scale_log2, int causal, int out_dtype, int cfg_id,
+                           void* workspace, size_t workspace_bytes, int device, void* stream) {
+  return fp8_attention_impl(q, k, v, out, BH, S_q, S_k, causal, D, q_strides, k_strides, v_strides, out_strides,
+                            scale_log2, out_dtype, cfg_id, workspace, workspace_bytes, device, stream);
 }
 
 }  // extern "C"

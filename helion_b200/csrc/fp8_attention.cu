@@ -76,7 +76,8 @@ __device__ __forceinline__ void reg_inc_softmax() {
 template <int D, int BN, bool V_KMAJOR, int OUT_DT, int POLY_OF8, bool LAZY>
 __global__ void __launch_bounds__(ATT_THREADS, (D == 64 && BN == 64) ? 4 : 2)
 fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                     const __grid_constant__ CUtensorMap tmap_v, void* out, int BH, int S, int64_t out_stride_bh,
+                     const __grid_constant__ CUtensorMap tmap_v, void* out, int BH, int S, int Sk, int causal_off,
+                     int64_t out_stride_bh,
                      int64_t out_stride_s, float scale_log2, uint32_t* status, unsigned int* sched) {
   using L = AttnLayout<D, BN>;
   constexpr int ST = L::KV_STAGES;
@@ -109,7 +110,20 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int m_tiles = (S + ATT_BM - 1) / ATT_BM;
-  const int n_steps = (S + ATT_BN - 1) / ATT_BN;
+  // S query rows, Sk keys.  causal_off < 0: no mask.  Otherwise query row i sees keys 0 .. i + causal_off
+  // (causal_off = Sk - S: the diagonal ends in the bottom-right corner), a tile only walks the key steps
+  // some of its rows can see, and tiles are handed out longest first within a batch*head slice.
+  const bool causal = causal_off >= 0;
+  const int n_steps_all = (Sk + ATT_BN - 1) / ATT_BN;
+  auto steps_of = [&](int mt) -> int {
+    if (!causal) return n_steps_all;
+    const int last_key = min(Sk - 1, mt * ATT_BM + ATT_BM - 1 + causal_off);
+    return last_key / ATT_BN + 1;
+  };
+  auto row_block_of = [&](int tile, int bh) -> int {
+    const int t = tile - bh * m_tiles;
+    return causal ? m_tiles - 1 - t : t;
+  };
   const int num_tiles = BH * m_tiles;
   const WaitCtx wctx{abort_flag, status};
 
@@ -172,7 +186,8 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             break;
           }
           const int bh = tile / m_tiles;
-          const int mt = tile - bh * m_tiles;
+          const int mt = row_block_of(tile, bh);
+          const int n_steps = steps_of(mt);
           mbar_arrive_expect_tx(q_full, L::Q_BYTES);
           tma_load_3d(smem + L::Q_OFFSET, &tmap_q, q_full, 0, mt * ATT_BM, bh);
           // the next tile: asked for now, needed after this tile's loads are issued
@@ -225,7 +240,9 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             ok = false;
             break;
           }
-          if (tile_q[tile_iter & 1u] < 0) break;  // no more tiles
+          const int tile = tile_q[tile_iter & 1u];
+          if (tile < 0) break;  // no more tiles
+          const int n_steps = steps_of(row_block_of(tile, tile / m_tiles));
           for (int j = 0; j < n_steps; ++j, ++g, slot_it += 2) {
             // waits for the K tile and for S to be free (the softmax warps have pulled step g-1 out)
             const uint32_t s = slot_it % ST;
@@ -273,6 +290,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           const int tile = tile_q[tile_iter & 1u];
           mbar_arrive(q_empty);  // this thread has the id (keeps q_full from running two phases ahead of it)
           if (tile < 0) break;
+          const int n_steps = steps_of(row_block_of(tile, tile / m_tiles));
           for (int j = 0; j < n_steps; ++j, ++g, slot_it += 2) {
             const uint32_t vs = (slot_it + 1) % ST;
             if (!mbar_wait_relaxed(&kv_full[vs], ((slot_it + 1) / ST) & 1u, wctx, SITE_ATTN_V_FULL, 100) ||
@@ -326,7 +344,10 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       mbar_arrive(q_empty);  // this thread has the id; the entry may be reused two tiles on
       if (tile < 0) break;
       const int bh = tile / m_tiles;
-      const int mt = tile - bh * m_tiles;
+      const int mt = row_block_of(tile, bh);
+      const int n_steps = steps_of(mt);
+      // keys this thread's row may see (all of them without a mask)
+      const int visible = causal ? mt * ATT_BM + row_in_tile + causal_off + 1 : Sk;
       float m_i = -INFINITY;
       float l_i = 0.0f;
       for (int j = 0; j < n_steps; ++j, ++g) {
@@ -342,7 +363,7 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         tc_fence_before_sync();
         mbar_arrive(s_free);  // S may be overwritten by the next Q K^T
 
-        const int valid = S - j * ATT_BN;  // keys of this step that exist
+        const int valid = min(Sk, visible) - j * ATT_BN;  // keys of this step that exist and that this row may see
         if (valid < ATT_BN) {
 #pragma unroll
           for (int c = 0; c < NC; ++c) {
@@ -544,7 +565,9 @@ int launch_attn_poly(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, c
   if (num_tiles > INT32_MAX) return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: too many tiles");
   const int grid = static_cast<int>(std::min<int64_t>(num_tiles, L::CTAS_PER_SM * ctx->num_sms));
   kernel<<<grid, ATT_THREADS, L::SMEM_BYTES, a.stream>>>(tq, tk, tv, a.out, static_cast<int>(a.BH),
-                                                         static_cast<int>(a.S), a.out_strides[0], a.out_strides[1],
+                                                         static_cast<int>(a.S), static_cast<int>(a.Sk),
+                                                         a.causal ? static_cast<int>(a.Sk - a.S) : -1, a.out_strides[0],
+                                                         a.out_strides[1],
                                                          a.scale_log2, ctx->status_dev, a.sched);
   HB_CUDA_CHECK(cudaGetLastError());
   return HB200_OK;
@@ -601,7 +624,7 @@ int attn_describe_config(int cfg_id, char* buf, int buf_len) {
 int launch_fp8_attention(const AttnArgs& args, DeviceCtx* ctx) {
   if (args.cfg_id >= kNumAttnConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_attention: no such config");
   AttnArgs a = args;
-  if (a.cfg_id < 0) a.cfg_id = attn_select_config(a.D, a.S);
+  if (a.cfg_id < 0) a.cfg_id = attn_select_config(a.D, a.Sk);
   const bool v_kmajor = a.v_strides[2] == 1 && a.v_strides[1] != 1;  // keys contiguous
   const uint32_t d = static_cast<uint32_t>(a.D);
   const CUtensorMapSwizzle swz_d = a.D == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
@@ -610,21 +633,22 @@ int launch_fp8_attention(const AttnArgs& args, DeviceCtx* ctx) {
   int rc;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(a.D), static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.BH)};
+    const uint64_t kdims[3] = {static_cast<uint64_t>(a.D), static_cast<uint64_t>(a.Sk), static_cast<uint64_t>(a.BH)};
     const uint32_t box[3] = {d, 128, 1};
     const uint32_t kvbox[3] = {d, bn, 1};
     const uint64_t qs[2] = {static_cast<uint64_t>(a.q_strides[1]), static_cast<uint64_t>(a.q_strides[0])};
     rc = encode_tmap_u8(&tq, a.q, 3, dims, qs, box, swz_d);
     if (rc != HB200_OK) return rc;
     const uint64_t ks[2] = {static_cast<uint64_t>(a.k_strides[1]), static_cast<uint64_t>(a.k_strides[0])};
-    rc = encode_tmap_u8(&tk, a.k, 3, dims, ks, kvbox, swz_d);
+    rc = encode_tmap_u8(&tk, a.k, 3, kdims, ks, kvbox, swz_d);
     if (rc != HB200_OK) return rc;
     if (!v_kmajor) {
       // physical [BH, S, D]: logical strides {bh, d, s} = {v_strides[0], 1, v_strides[2]}
       const uint64_t vs[2] = {static_cast<uint64_t>(a.v_strides[2]), static_cast<uint64_t>(a.v_strides[0])};
-      rc = encode_tmap_u8(&tv, a.v, 3, dims, vs, kvbox, swz_d);
+      rc = encode_tmap_u8(&tv, a.v, 3, kdims, vs, kvbox, swz_d);
       if (rc != HB200_OK) return rc;
     } else {
-      const uint64_t vdims[3] = {static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.D), static_cast<uint64_t>(a.BH)};
+      const uint64_t vdims[3] = {static_cast<uint64_t>(a.Sk), static_cast<uint64_t>(a.D), static_cast<uint64_t>(a.BH)};
       const uint32_t vbox[3] = {bn, d, 1};
       const uint64_t vs[2] = {static_cast<uint64_t>(a.v_strides[1]), static_cast<uint64_t>(a.v_strides[0])};
       rc = encode_tmap_u8(&tv, a.v, 3, vdims, vs, vbox,

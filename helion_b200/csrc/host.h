@@ -113,7 +113,9 @@ struct AttnArgs {
   const void* k;
   const void* v;
   void* out;
-  int64_t BH, S, D;
+  int64_t BH, S, D;        // S = query rows per slice
+  int64_t Sk = 0;          // keys per slice (= S for the reference's square problem)
+  int causal = 0;          // hide key j from query i when j > i + (Sk - S)
   int64_t q_strides[3];
   int64_t k_strides[3];
   int64_t v_strides[3];    // logical [BH, D, S]

@@ -138,14 +138,17 @@ def fp8_attention(
     config: Optional[int] = None,
     out: Optional[torch.Tensor] = None,
     balanced: Optional[bool] = None,
+    causal: bool = False,
 ) -> torch.Tensor:
-    """Non-causal FP8 attention forward with the reference's numerics.
+    """FP8 attention forward with the reference's numerics (non-causal unless ``causal=True``).
 
     Same contract as the reference's ``fp8_attention_kernel(q, k, v, batch, heads)``
     (examples/fp8_attention.py:22-106): ``q``, ``k`` are ``[batch*heads, seq, dim]`` e4m3, ``v`` is
     the "pre-transposed" ``[batch*heads, dim, seq]`` e4m3 tensor (either physical layout), the
     result is ``[batch, heads, seq, dim]`` e4m3.  ``out_dtype`` (e4m3 / bf16 / fp32), ``config``,
-    ``out`` and ``balanced`` (see :func:`attention_into`) are keyword-only extensions.
+    ``out`` and ``balanced`` (see :func:`attention_into`) are keyword-only extensions.  Two more go
+    beyond the reference's kernel: ``k`` / ``v`` may hold a different number of keys than ``q`` has
+    rows, and ``causal=True`` hides key j from query i when ``j > i + (seq_k - seq_q)``.
     """
     for name, t in (("q", q), ("k", k), ("v", v)):
         if t.dtype != torch.float8_e4m3fn:
@@ -153,7 +156,8 @@ def fp8_attention(
         if t.dim() != 3:
             raise ValueError(f"fp8_attention expects 3-D inputs, {name} has shape {tuple(t.shape)}")
     bh, s, d = q.shape
-    if tuple(k.shape) != (bh, s, d) or tuple(v.shape) != (bh, d, s):
+    sk = k.shape[1]
+    if tuple(k.shape) != (bh, sk, d) or tuple(v.shape) != (bh, d, sk):
         raise ValueError(
             f"fp8_attention shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)} "
             "(expected [BH,S,D], [BH,S,D], [BH,D,S])"
@@ -175,13 +179,13 @@ def fp8_attention(
         raise ValueError("fp8_attention: `out` must be a contiguous [batch, heads, seq, dim] tensor of out_dtype")
     if bh == 0 or s == 0:
         return out
-    attention_into(q, k, v, out.view(bh, s, d), config=config, balanced=balanced)
+    attention_into(q, k, v, out.view(bh, s, d), config=config, balanced=balanced, causal=causal)
     return out
 
 
 def attention_into(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out3: torch.Tensor, *, config: Optional[int] = None,
-    balanced: Optional[bool] = None,
+    balanced: Optional[bool] = None, causal: bool = False,
 ) -> None:
     """Launch the attention kernel on ``[BH,S,D]`` / ``[BH,D,S]`` tensors, writing ``out3 [BH,S,D]``.
 
@@ -202,9 +206,18 @@ def attention_into(
     arr = ctypes.c_int64 * 3
     lib = _lib.load()
     cfg = -1 if config is None else int(config)
+    sk = k.shape[1]
     if balanced is None:
-        balanced = s >= 2048
-    if balanced:
+        balanced = sk >= 2048 or (causal and sk >= 512)  # masked tiles differ in length: balance earlier
+    if causal or sk != s:
+        ws = torch.empty(_lib.ATTN_WORKSPACE_BYTES, dtype=torch.uint8, device=q.device) if balanced else None
+        code = lib.hb200_fp8_attention_ex(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out3.data_ptr(), bh, s, sk, d,
+            arr(*q.stride()), arr(*k.stride()), arr(*v.stride()), arr(*out3.stride()),
+            scale_log2, int(bool(causal)), _OUT_DT[out3.dtype], cfg,
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, dev, _stream_ptr(dev),
+        )
+    elif balanced:
         ws = torch.empty(_lib.ATTN_WORKSPACE_BYTES, dtype=torch.uint8, device=q.device)
         code = lib.hb200_fp8_attention_ws(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out3.data_ptr(), bh, s, d,

@@ -150,6 +150,22 @@ HB200_API int hb200_fp8_attention_ws(const void* q, const void* k, const void* v
                            int out_dtype, int cfg_id, void* workspace, size_t workspace_bytes, int device,
                            void* stream);
 
+/* hb200_fp8_attention_ws with two extensions the reference's fp8 kernel does not have (its bf16 sibling
+ * examples/attention.py:51-58 takes seq_k != seq_q; neither has a mask): k and v may hold S_k keys while q
+ * holds S_q rows per slice, and causal != 0 hides key j from query i when j > i + (S_k - S_q) -- the
+ * diagonal ends in the bottom-right corner, every query sees at least key 0, S_k >= S_q is required.
+ * A hidden score counts as -inf before the row max, like the padding of a ragged key tile; tiles skip
+ * the key steps none of their rows can see and are handed out longest first.
+ *   q [BH, S_q, D], k [BH, S_k, D], v logical [BH, D, S_k], out [BH, S_q, D]; strides as for
+ *   hb200_fp8_attention; S_q % 16 == 0, S_k % 16 == 0.
+ *   workspace: NULL (fixed tile order) or HB200_ATTN_WORKSPACE_BYTES as for hb200_fp8_attention_ws
+ *   (recommended with a mask: the tiles of a slice differ in length). */
+HB200_API int hb200_fp8_attention_ex(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S_q,
+                           int64_t S_k, int64_t D, const int64_t q_strides[3], const int64_t k_strides[3],
+                           const int64_t v_strides[3], const int64_t out_strides[3], float scale_log2, int causal,
+                           int out_dtype, int cfg_id, void* workspace, size_t workspace_bytes, int device,
+                           void* stream);
+
 /* q, k, v -> float8_e4m3fn in one launch: the three casts of preprocess_fp8_attention_inputs
  * (examples/fp8_attention.py:125-128; the permute and reshapes of :127-132 only change strides, so
  * the caller does them as views).  Each of q, k, v holds `count` contiguous elements of src_dtype

@@ -185,6 +185,50 @@ def test_default_row_for_long_sequences_at_head_dim_64(hb):
     assert torch.equal(hb.fp8_attention(qd, kd, vd, 1, 2), hb.fp8_attention(qd, kd, vd, 1, 2, config=0))
 
 
+@pytest.mark.parametrize("config", [None, 0, 1, 4])
+@pytest.mark.parametrize(
+    "batch,heads,sq,sk,dim,causal",
+    [(1, 2, 256, 256, 64, True), (2, 3, 512, 512, 128, True), (1, 2, 128, 384, 64, False), (1, 2, 128, 384, 64, True),
+     (1, 1, 80, 208, 128, True), (1, 2, 1024, 1040, 64, True), (2, 2, 16, 16, 64, True), (1, 1, 384, 144, 128, False)],
+)
+def test_seq_k_differs_and_causal_mask(hb, batch, heads, sq, sk, dim, causal, config):
+    """hb200_fp8_attention_ex: k / v with their own length and the bottom-right-aligned causal mask.
+    Neither exists in the reference's fp8 kernel, so the oracle's extension of the reference's loop (a
+    hidden score is -inf before the row max) is the yardstick: same blocking near bit-exact, single
+    tile within the stated tolerance.  Tiles skip the key steps they cannot see; both tile orders and
+    both layouts of v must agree bit for bit."""
+    g = torch.Generator().manual_seed(sq + sk + dim)
+    q8, k8, v8 = (torch.randn(batch * heads, n, dim, generator=g).to(torch.float8_e4m3fn) for n in (sq, sk, sk))
+    vb = v8.permute(0, 2, 1)
+    _, one_raw = o.fp8_attention(bits(q8), bits(k8), bits(vb), batch, heads, return_parts=True, causal=causal)
+    got = hb.fp8_attention(q8.cuda(), k8.cuda(), v8.cuda().permute(0, 2, 1), batch, heads, out_dtype=torch.float32,
+                           config=config, causal=causal)
+    assert tuple(got.shape) == (batch, heads, sq, dim) and torch.isfinite(got).all()
+    np.testing.assert_allclose(got.cpu().numpy(), one_raw, rtol=2e-2, atol=2.5e-2 if config == 1 else 2e-2)
+    if config != 1:  # the exact rows: the oracle walking the same key blocks
+        bn = 64 if (dim == 64 and (config == 4 or (config is None and sk >= 2048))) else 128
+        blk8, blk_raw = o.fp8_attention(bits(q8), bits(k8), bits(vb), batch, heads, return_parts=True, block_n=bn,
+                                        causal=causal)
+        out8 = bits(hb.fp8_attention(q8.cuda(), k8.cuda(), v8.cuda().permute(0, 2, 1), batch, heads, config=config,
+                                     causal=causal))
+        assert_near_bit_exact(got.cpu().numpy(), out8, blk_raw, blk8)
+    for balanced in (False, True):
+        again = hb.fp8_attention(q8.cuda(), k8.cuda(), v8.cuda().permute(0, 2, 1).contiguous(), batch, heads,
+                                 out_dtype=torch.float32, config=config, causal=causal, balanced=balanced)
+        assert torch.equal(again, got)
+    torch.cuda.synchronize()
+    _lib.check_status(0)
+
+
+def test_causal_needs_enough_keys(hb):
+    q = torch.zeros(1, 256, 64, device="cuda").to(torch.float8_e4m3fn)
+    k = torch.zeros(1, 128, 64, device="cuda").to(torch.float8_e4m3fn)
+    with pytest.raises(ValueError, match="seq_k >= seq_q"):
+        hb.fp8_attention(q, k, k.permute(0, 2, 1), 1, 1, causal=True)
+    out = hb.fp8_attention(q, k, k.permute(0, 2, 1), 1, 1)  # fine without the mask
+    assert tuple(out.shape) == (1, 1, 256, 64)
+
+
 def test_balanced_entry_rejects_a_bad_workspace(hb, built_library):
     import ctypes
 
