@@ -524,6 +524,13 @@ def make_workload(name: str, torch, dev, hb, config=None):
         outg = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         return (lambda: hb.fp8_gemm(xa, ya, out_dtype=torch.bfloat16, out=outg, config=config, scale_a=sa, scale_b=sb),
                 GEMM_FLOPS, M * K + K * N + 2 * M * N + 4 * (M + N))
+    if name.startswith("attn_bf16_") or name.startswith("sdpa_bf16_"):  # the 16-bit sibling (examples/attention.py); torch SDPA for context
+        b, h, s, d = ATTN_SHAPES["attn_" + name[len("attn_bf16_"):]]
+        g = torch.Generator(device=dev).manual_seed(6)
+        q, k, v = (torch.randn(b, h, s, d, device=dev, generator=g).to(torch.bfloat16) for _ in range(3))
+        fn = (lambda: hb.attention(q, k, v)) if name.startswith("attn_") else (
+            lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v))
+        return fn, 4.0 * b * h * s * s * d, 2 * 4 * b * h * s * d
     if name == "matmul_bf16_8192":  # hb200_gemm_16bit: the reference's examples/matmul.py shape class, row-major y
         g = torch.Generator(device=dev).manual_seed(5)
         xa = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
@@ -541,8 +548,10 @@ def make_workload(name: str, torch, dev, hb, config=None):
 
 
 PREPROCESS = [f"preprocess_{n[len('attn_'):]}" for n in ATTN_SHAPES]
+ATTN16 = [f"attn_bf16_{n[len('attn_'):]}" for n in ATTN_SHAPES]
+SDPA16 = [f"sdpa_bf16_{n[len('attn_'):]}" for n in ATTN_SHAPES]
 CAUSAL = [f"attn_causal_{n[len('attn_'):]}" for n in ATTN_SHAPES]
-WORKLOADS = ["gemm_8192", *ATTN_SHAPES, *CAUSAL, *(f"mlp_M{m}" for m in MLP_M), "cublaslt_8192", "gemm_8192_rowwise_scaled",
+WORKLOADS = ["gemm_8192", *ATTN_SHAPES, *CAUSAL, *ATTN16, *SDPA16, *(f"mlp_M{m}" for m in MLP_M), "cublaslt_8192", "gemm_8192_rowwise_scaled",
              "matmul_bf16_8192", *PREPROCESS]
 
 
@@ -583,6 +592,15 @@ def run_extras(hb, _lib, o, torch, dev, flush, fp8_peak, peaks) -> dict:
     res["matmul_bf16_8192_bias_relu"] = {"ms": e["ms"], "ms_min": e["ms_min"], "tflops": e["tflops"],
                                          "frac_of_measured_bf16_peak": e["tflops"] / peaks["bf16_tflops"],
                                          "frac_of_nominal_2250": e["tflops"] / 2250.0}
+    res["attention_bf16"] = {}
+    for name, ctx_name in zip(ATTN16, SDPA16):
+        e = entry(name)
+        item = {"ms": e["ms"], "tflops": e["tflops"], "frac_of_measured_bf16_peak": e["tflops"] / peaks["bf16_tflops"]}
+        try:  # context only: torch's scaled_dot_product_attention on the same tensors
+            item["torch_sdpa_ms"] = entry(ctx_name)["ms"]
+        except Exception as ex:
+            item["torch_sdpa_error"] = str(ex)[:100]
+        res["attention_bf16"][name] = item
     res["attention_preprocess_fp16"] = {}
     for name in PREPROCESS:
         e = entry(name)

@@ -66,6 +66,11 @@ SIGNATURES = {
         [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64x3, _i64x3, _i64x3, _i64x3, ctypes.c_float, ctypes.c_int,
          ctypes.c_int, ctypes.c_int, _vp, ctypes.c_size_t, ctypes.c_int, _vp],
     ),
+    "hb200_attention_16bit": (
+        ctypes.c_int,
+        [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64x3, _i64x3, _i64x3, _i64x3, ctypes.c_float, ctypes.c_int,
+         ctypes.c_int, _vp, ctypes.c_size_t, ctypes.c_int, _vp],
+    ),
     "hb200_fp8_attention_preprocess": (
         ctypes.c_int,
         [_vp, _vp, _vp, _vp, _vp, _vp, _i64, ctypes.c_int, ctypes.c_int, _vp],

@@ -548,6 +548,76 @@ int hb200_fp8_attention(const void* q, const void* k, const void* v, void* out, 
                             out_dtype, cfg_id, nullptr, 0, device, stream);
 }
 
+int hb200_attention_16bit(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S_q, int64_t S_k,
+                          int64_t D, const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                          const int64_t out_strides[3], float scale_log2, int in_dtype, int out_dtype, void* workspace,
+                          size_t workspace_bytes, int device, void* stream) {
+  if (in_dtype != HB200_DT_FP16 && in_dtype != HB200_DT_BF16) {
+    return set_error(HB200_ERR_BAD_DTYPE, "attention_16bit: in_dtype must be FP16 or BF16");
+  }
+  if (out_dtype != in_dtype && out_dtype != HB200_DT_FP32) {
+    return set_error(HB200_ERR_BAD_DTYPE, "attention_16bit: out_dtype must be the operands' dtype or FP32");
+  }
+  if (D != 64 && D != 128) return set_error(HB200_ERR_BAD_SHAPE, "attention_16bit: head_dim must be 64 or 128");
+  if (BH < 1 || S_q < 1 || S_k < 1 || BH > INT32_MAX || S_q > INT32_MAX || S_k > INT32_MAX) {
+    return set_error(HB200_ERR_BAD_SHAPE, "attention_16bit: batch*heads, seq_q and seq_k must be in [1, 2^31)");
+  }
+  if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || q_strides == nullptr || k_strides == nullptr ||
+      v_strides == nullptr || out_strides == nullptr) {
+    return set_error(HB200_ERR_ALIGN, "attention_16bit: null pointer");
+  }
+  if (q_strides[2] != 1 || k_strides[2] != 1 || v_strides[2] != 1 || out_strides[2] != 1) {
+    return set_error(HB200_ERR_BAD_STRIDE, "attention_16bit: q, k, v and out need a unit head_dim stride");
+  }
+  const int64_t* in_strides[3] = {q_strides, k_strides, v_strides};
+  for (const int64_t* st : in_strides) {
+    if (st[1] < D || st[1] % 8 != 0 || st[0] % 8 != 0) {
+      return set_error(HB200_ERR_BAD_STRIDE, "attention_16bit: row and slice strides must be multiples of 8 and rows >= D");
+    }
+  }
+  const int64_t out_elem = out_dtype == HB200_DT_FP32 ? 4 : 2;
+  if (out_strides[1] < D || (out_strides[1] * out_elem) % 16 != 0 || (out_strides[0] * out_elem) % 16 != 0) {
+    return set_error(HB200_ERR_BAD_STRIDE, "attention_16bit: out rows must be 16-byte aligned");
+  }
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(out)) & 15u) {
+    return set_error(HB200_ERR_ALIGN, "attention_16bit: q, k, v and out must be 16-byte aligned");
+  }
+  DeviceCtx* ctx = get_device_ctx(device);
+  if (ctx == nullptr) return ctx_error_code(device);
+  AttnArgs a;
+  a.q = q;
+  a.k = k;
+  a.v = v;
+  a.out = out;
+  a.BH = BH;
+  a.S = S_q;
+  a.Sk = S_k;
+  a.D = D;
+  for (int i = 0; i < 3; ++i) {
+    a.q_strides[i] = q_strides[i];
+    a.k_strides[i] = k_strides[i];
+    a.v_strides[i] = v_strides[i];
+    a.out_strides[i] = out_strides[i];
+  }
+  a.scale_log2 = scale_log2;
+  a.out_dtype = out_dtype;
+  a.cfg_id = -1;
+  a.device = device;
+  a.stream = static_cast<cudaStream_t>(stream);
+  a.sched = nullptr;
+  a.kind = in_dtype == HB200_DT_FP16 ? 1 : 2;
+  DeviceGuard guard(device);
+  if (workspace != nullptr) {
+    if (workspace_bytes < HB200_ATTN_WORKSPACE_BYTES || (reinterpret_cast<uintptr_t>(workspace) & 15u)) {
+      return set_error(HB200_ERR_WORKSPACE, "attention_16bit: workspace must be 16-byte aligned and hold HB200_ATTN_WORKSPACE_BYTES");
+    }
+    HB_CUDA_CHECK(cudaMemsetAsync(workspace, 0, HB200_ATTN_WORKSPACE_BYTES, a.stream));
+    a.sched = static_cast<unsigned int*>(workspace);
+  }
+  return launch_attention_16bit(a, ctx);
+}
+
 int hb200_fp8_attention_preprocess(const void* q, const void* k, const void* v, void* q8, void* k8, void* v8,
                                    int64_t count, int src_dtype, int device, void* stream) {
   if (src_dtype != HB200_DT_FP16 && src_dtype != HB200_DT_BF16 && src_dtype != HB200_DT_FP32) {

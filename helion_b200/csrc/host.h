@@ -116,6 +116,7 @@ struct AttnArgs {
   int64_t BH, S, D;        // S = query rows per slice
   int64_t Sk = 0;          // keys per slice (= S for the reference's square problem)
   int causal = 0;          // hide key j from query i when j > i + (Sk - S)
+  int kind = 0;            // 0 = e4m3; 1 = fp16, 2 = bf16 (attention_16bit.cu: v is then [BH, Sk, D], strides {bh, s, d})
   int64_t q_strides[3];
   int64_t k_strides[3];
   int64_t v_strides[3];    // logical [BH, D, S]
@@ -129,6 +130,8 @@ struct AttnArgs {
 };
 
 int launch_fp8_attention(const AttnArgs& args, DeviceCtx* ctx);
+// fp16 / bf16 attention (attention_16bit.cu); args.kind, args.Sk and args.sched are honoured, args.cfg_id is not.
+int launch_attention_16bit(const AttnArgs& args, DeviceCtx* ctx);
 // q, k, v (fp16 / bf16 / fp32, `count` elements each) -> e4m3fn with torch's cast rule (quantize.cu).
 int launch_attention_preprocess(const void* q, const void* k, const void* v, void* q8, void* k8, void* v8, int64_t count,
                                 int src_dtype, DeviceCtx* ctx, cudaStream_t stream);

@@ -321,3 +321,54 @@ def matmul(
     )
     _lib.raise_for(code, "matmul")
     return out
+
+
+def attention(
+    q_in: torch.Tensor,
+    k_in: torch.Tensor,
+    v_in: torch.Tensor,
+    *,
+    out_dtype: Optional[torch.dtype] = None,
+    balanced: Optional[bool] = None,
+) -> torch.Tensor:
+    """``softmax(q k^T / sqrt(D)) v`` for fp16 or bf16 ``q [..., Sq, D]``, ``k``, ``v [..., Sk, D]``.
+
+    Same contract as the reference's ``attention(q_in, k_in, v_in)`` (examples/attention.py:29-84): leading
+    dimensions are flattened into independent slices, the result has ``q_in``'s shape and dtype (fp32 with
+    ``out_dtype=torch.float32``), and the intermediate roundings are those of the reference's 16-bit tensors.
+    """
+    if not (q_in.dtype == k_in.dtype == v_in.dtype) or q_in.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(f"attention expects three float16 or three bfloat16 tensors, got {q_in.dtype}, {k_in.dtype}, {v_in.dtype}")
+    if q_in.dim() < 2 or k_in.dim() != q_in.dim() or v_in.dim() != q_in.dim():
+        raise ValueError("attention expects q [..., Sq, D], k [..., Sk, D], v [..., Sk, D]")
+    m_dim, d = q_in.shape[-2], q_in.shape[-1]
+    n_dim = k_in.shape[-2]
+    assert n_dim == v_in.size(-2)  # examples/attention.py:52
+    assert d == k_in.size(-1) == v_in.size(-1)  # examples/attention.py:54
+    if k_in.shape[:-2] != q_in.shape[:-2] or v_in.shape[:-2] != q_in.shape[:-2]:
+        raise ValueError("attention: q, k and v must agree in their leading (batch) dimensions")
+    out_dtype = q_in.dtype if out_dtype is None else out_dtype
+    if out_dtype not in (q_in.dtype, torch.float32):
+        raise TypeError(f"attention out_dtype must be {q_in.dtype} or float32, got {out_dtype}")
+    dev = _require_cuda(q_in, k_in, v_in)
+    q, k, v = (t.reshape(-1, t.shape[-2], d) for t in (q_in, k_in, v_in))
+    q, k, v = (t if t.stride(2) == 1 else t.contiguous() for t in (q, k, v))
+    bh = q.shape[0]
+    out = torch.empty((bh, m_dim, d), dtype=out_dtype, device=q.device)
+    if bh == 0 or m_dim == 0:
+        return out.view(q_in.shape)
+    if n_dim == 0:
+        raise ValueError("attention: k and v hold no keys")
+    scale_log2 = (1.0 / math.sqrt(float(d))) * 1.44269504  # qk_scale of examples/attention.py:60-61
+    if balanced is None:
+        balanced = n_dim >= 2048
+    ws = torch.empty(_lib.ATTN_WORKSPACE_BYTES, dtype=torch.uint8, device=q.device) if balanced else None
+    arr = ctypes.c_int64 * 3
+    code = _lib.load().hb200_attention_16bit(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), bh, m_dim, n_dim, d,
+        arr(*q.stride()), arr(*k.stride()), arr(*v.stride()), arr(*out.stride()), scale_log2,
+        _OUT_DT[q_in.dtype], _OUT_DT[out_dtype], ws.data_ptr() if ws is not None else None,
+        ws.numel() if ws is not None else 0, dev, _stream_ptr(dev),
+    )
+    _lib.raise_for(code, "attention")
+    return out.view(q_in.shape)

@@ -166,6 +166,21 @@ HB200_API int hb200_fp8_attention_ex(const void* q, const void* k, const void* v
                            int out_dtype, int cfg_id, void* workspace, size_t workspace_bytes, int device,
                            void* stream);
 
+/* out[bh] = cast(softmax(q[bh] k[bh]^T / sqrt(D)) v[bh]) for fp16 or bf16 q [BH, S_q, D], k and v [BH, S_k, D]
+ * (head_dim contiguous; strides {bh, s, d} in elements), out [BH, S_q, D], non-causal.  Replaces the device
+ * kernel of the reference's examples/attention.py:29-84 (`attention(q_in, k_in, v_in)`) with its ref-eager
+ * numerics: q k^T rounded to the operands' 16-bit type (torch.bmm of 16-bit tensors), times
+ * scale_log2 = log2(e)/sqrt(D) rounded to 16 bits again, running max / exp2 / row sum in fp32, P cast to 16
+ * bits for P V, fp32 accumulation, division by the row sum, cast to the operands' type.
+ *   in_dtype: HB200_DT_FP16 or HB200_DT_BF16; out_dtype: the same, or HB200_DT_FP32.
+ *   D in {64, 128}; S_q, S_k >= 1 (any: ragged tiles are zero-filled and masked); strides multiples of 8.
+ *   workspace: NULL (fixed tile order) or HB200_ATTN_WORKSPACE_BYTES for the balanced tile order, as for
+ *   hb200_fp8_attention_ws. */
+HB200_API int hb200_attention_16bit(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S_q,
+                          int64_t S_k, int64_t D, const int64_t q_strides[3], const int64_t k_strides[3],
+                          const int64_t v_strides[3], const int64_t out_strides[3], float scale_log2, int in_dtype,
+                          int out_dtype, void* workspace, size_t workspace_bytes, int device, void* stream);
+
 /* q, k, v -> float8_e4m3fn in one launch: the three casts of preprocess_fp8_attention_inputs
  * (examples/fp8_attention.py:125-128; the permute and reshapes of :127-132 only change strides, so
  * the caller does them as views).  Each of q, k, v holds `count` contiguous elements of src_dtype

@@ -147,3 +147,30 @@ def test_matmul_16bit_oracle_against_torch(dtype):
         np.testing.assert_allclose(got, want.to(dtype).float().numpy(), rtol=2 ** -7 if name == "bf16" else 2 ** -10, atol=1e-3)
     with pytest.raises(AssertionError, match="size mismatch"):
         o.matmul_16bit(np.zeros((4, 8), np.float32), np.zeros((16, 4), np.float32))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+def test_attention_16bit_oracle_against_torch(dtype):
+    """examples/attention.py cannot run in ref-eager mode on a CPU either (aten::bmm.dtype is CUDA-only),
+    so its restatement is checked against the same sequence of eager torch operations written with
+    ``bmm(...).float()`` in place of the mixed-precision baddbmm, and against exact softmax attention."""
+    import math
+
+    g = torch.Generator().manual_seed(4)
+    q, k, v = (torch.randn(2, n, 64, generator=g).to(dtype) for n in (48, 80, 80))
+    name = "fp16" if dtype == torch.float16 else "bf16"
+    qk_scale = (1.0 / math.sqrt(64.0)) * 1.44269504
+    qk = torch.bmm(q, k.transpose(1, 2))
+    m = torch.amax(qk, -1).float() * 0 + (torch.amax(qk, -1) * qk_scale).float()
+    x = (qk * qk_scale).float() - m[:, :, None]
+    p = torch.exp2(x)
+    l = p.sum(-1)
+    acc = torch.bmm(p.to(dtype).float(), v.float())
+    want = (acc / l[:, :, None]).to(dtype)
+    got = o.attention_16bit(q.float().numpy(), k.float().numpy(), v.float().numpy(), name)
+    ulp = 2.0 ** -7 if name == "bf16" else 2.0 ** -10
+    np.testing.assert_allclose(got, want.float().numpy(), rtol=2 * ulp, atol=1e-3)
+    exact = torch.softmax((q.double() @ k.double().transpose(1, 2)) / 8.0, -1) @ v.double()
+    np.testing.assert_allclose(got, exact.float().numpy(), rtol=2e-2, atol=2e-2)
+    blocked = o.attention_16bit(q.float().numpy(), k.float().numpy(), v.float().numpy(), name, block_n=32)
+    np.testing.assert_allclose(blocked, got, rtol=2e-2, atol=2e-2)
