@@ -49,11 +49,18 @@ struct Attn16Layout {
   static_assert(SMEM_BYTES <= 112 * 1024, "two CTAs must fit one SM");
 };
 
-// fp32 -> the operands' 16-bit type and back: the value a 16-bit torch tensor would hold
+// Two fp32 values -> rounded to the 16-bit type -> back to fp32, with one packed conversion.
 template <int KIND>
-__device__ __forceinline__ float round16(float x) {
-  if constexpr (KIND == KIND_F16) return __half2float(__float2half_rn(x));
-  else return __bfloat162float(__float2bfloat16_rn(x));
+__device__ __forceinline__ void round16_pair(float& a, float& b) {
+  if constexpr (KIND == KIND_F16) {
+    const float2 f = __half22float2(__floats2half2_rn(a, b));
+    a = f.x;
+    b = f.y;
+  } else {
+    const uint32_t w = pack_bf16x2(a, b);  // a in the low half
+    a = __uint_as_float(w << 16);
+    b = __uint_as_float(w & 0xffff0000u);
+  }
 }
 
 template <int KIND>
@@ -318,21 +325,41 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         // t = cast16(cast16(qk) * c): the two 16-bit roundings of the reference's tensors; keys beyond
         // seq_k count as -inf
         const int valid = Sk - j * A16_BN;
-        float mx = -INFINITY;
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;  // independent chains
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float t = round16<KIND>(round16<KIND>(__uint_as_float(s[c][i])) * scale_log2);
-            if (c * 32 + i >= valid) t = -INFINITY;
-            s[c][i] = __float_as_uint(t);
-            mx = fmaxf(mx, t);
+          for (int i = 0; i < 32; i += 4) {
+            float t0 = __uint_as_float(s[c][i]), t1 = __uint_as_float(s[c][i + 1]);
+            float t2 = __uint_as_float(s[c][i + 2]), t3 = __uint_as_float(s[c][i + 3]);
+            round16_pair<KIND>(t0, t1);
+            round16_pair<KIND>(t2, t3);
+            t0 *= scale_log2;
+            t1 *= scale_log2;
+            t2 *= scale_log2;
+            t3 *= scale_log2;
+            round16_pair<KIND>(t0, t1);
+            round16_pair<KIND>(t2, t3);
+            if (valid < A16_BN) {  // ragged last step only
+              if (c * 32 + i >= valid) t0 = -INFINITY;
+              if (c * 32 + i + 1 >= valid) t1 = -INFINITY;
+              if (c * 32 + i + 2 >= valid) t2 = -INFINITY;
+              if (c * 32 + i + 3 >= valid) t3 = -INFINITY;
+            }
+            s[c][i] = __float_as_uint(t0);
+            s[c][i + 1] = __float_as_uint(t1);
+            s[c][i + 2] = __float_as_uint(t2);
+            s[c][i + 3] = __float_as_uint(t3);
+            mx0 = fmaxf(mx0, t0);
+            mx1 = fmaxf(mx1, t1);
+            mx2 = fmaxf(mx2, t2);
+            mx3 = fmaxf(mx3, t3);
           }
         }
-        const float m_new = fmaxf(m_i, mx);
+        const float m_new = fmaxf(m_i, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
         const bool moved = m_new > m_i;
         const float alpha = fast_exp2(m_i - m_new);
-        float sum = 0.0f;
+        float sum0 = 0.0f, sum1 = 0.0f;
         uint32_t packed[32];
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -340,11 +367,12 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           for (int i = 0; i < 32; i += 2) {
             const float p0 = fast_exp2(__uint_as_float(s[c][i]) - m_new);
             const float p1 = fast_exp2(__uint_as_float(s[c][i + 1]) - m_new);
-            sum += p0 + p1;
+            sum0 += p0;
+            sum1 += p1;
             packed[c * 16 + i / 2] = pack16x2<KIND>(p0, p1);
           }
         }
-        l_i = l_i * alpha + sum;
+        l_i = l_i * alpha + (sum0 + sum1);
 
         if (g > 0) {
           ok = mbar_wait(pv_done, (g - 1u) & 1u, wctx, SITE_ATTN_PV_DONE);

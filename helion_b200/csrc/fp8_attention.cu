@@ -1,5 +1,6 @@
-// FP8 attention forward (non-causal) for sm_100a with the numerics of pytorch-labs/helion's
-// examples/fp8_attention.py:54-105:
+// FP8 attention forward for sm_100a with the numerics of pytorch-labs/helion's
+// examples/fp8_attention.py:54-105 (non-causal, seq_k = seq_q there; a separate key length and a
+// bottom-right-aligned causal mask are extensions, see steps_of / `visible` below):
 //   s = (q k^T) * c            e4m3 x e4m3 -> fp32,  c = log2(e)/sqrt(D)
 //   m = running row max, p = exp2(s - m), l = l*alpha + rowsum(p)   (fp32, online softmax)
 //   acc = acc*alpha + e4m3(p) v                                     (P cast to e4m3 un-normalised)

@@ -5,7 +5,6 @@ from __future__ import annotations
 import os
 import socket
 
-import numpy as np
 import pytest
 import torch
 import torch.distributed as dist
