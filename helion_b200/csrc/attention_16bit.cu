@@ -433,10 +433,9 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             uint32_t w[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              // product with the correctly rounded reciprocal: within 2 fp32 ulps of the quotient, i.e. a
-              // different 16-bit result with probability ~2^-11 (fp16) / 2^-14 (bf16) per element
-              const float lo = __uint_as_float(o[2 * i]) * inv_l;
-              const float hi = __uint_as_float(o[2 * i + 1]) * inv_l;
+              // through the rounded reciprocal with one residual correction instead of an IEEE division
+              const float lo = div_by_rcp(__uint_as_float(o[2 * i]), l_i, inv_l);
+              const float hi = div_by_rcp(__uint_as_float(o[2 * i + 1]), l_i, inv_l);
               w[i] = OUT_DT == HB200_DT_FP16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
             }
             uint16_t* dst = reinterpret_cast<uint16_t*>(out) + out_off + c * 32;

@@ -484,6 +484,15 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// a / b from the correctly rounded reciprocal r = 1/b in three instructions: one residual correction of
+// the product a*r.  The result is within a small fraction of an ulp of the rounded quotient (it equals
+// it except in rare double-rounding cases), at a tenth of the instructions of an IEEE division.
+__device__ __forceinline__ float div_by_rcp(float a, float b, float r) {
+  const float q = a * r;
+  const float e = fmaf(-q, b, a);
+  return fmaf(e, r, q);
+}
+
 // Two floats -> two e4m3 bytes (lo in bits 0-7), round-to-nearest-even, saturating to +-448.
 __device__ __forceinline__ uint16_t pack_e4m3x2(float lo, float hi) {
   uint16_t r;

@@ -466,9 +466,9 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tc_fence_after_sync();
       const int row = mt * ATT_BM + row_in_tile;
       const int64_t out_off = static_cast<int64_t>(bh) * out_stride_bh + static_cast<int64_t>(row) * out_stride_s;
-      // The 8- and 16-bit outputs multiply by the correctly rounded reciprocal instead of dividing: the
-      // product is within 2 fp32 ulps of the quotient, which changes a rounded output with probability
-      // ~2^-19 (e4m3) / 2^-14 (bf16) per element and saves ~10 instructions per element; fp32 output divides.
+      // The 8- and 16-bit outputs divide through the correctly rounded reciprocal with one residual
+      // correction (div_by_rcp): an IEEE division costs ~30 instructions per element, 64-128 of them per
+      // row; the fp32 output keeps the IEEE division.
       const float inv_l = __frcp_rn(l_i);
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
@@ -480,8 +480,10 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             uint32_t w[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              w[i] = pack_e4m3x4(__uint_as_float(o[4 * i]) * inv_l, __uint_as_float(o[4 * i + 1]) * inv_l,
-                                 __uint_as_float(o[4 * i + 2]) * inv_l, __uint_as_float(o[4 * i + 3]) * inv_l);
+              w[i] = pack_e4m3x4(div_by_rcp(__uint_as_float(o[4 * i]), l_i, inv_l),
+                                 div_by_rcp(__uint_as_float(o[4 * i + 1]), l_i, inv_l),
+                                 div_by_rcp(__uint_as_float(o[4 * i + 2]), l_i, inv_l),
+                                 div_by_rcp(__uint_as_float(o[4 * i + 3]), l_i, inv_l));
             }
             uint8_t* dst = reinterpret_cast<uint8_t*>(out) + out_off + c * 32;
             *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -490,7 +492,8 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             uint32_t w[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              w[i] = pack_bf16x2(__uint_as_float(o[2 * i]) * inv_l, __uint_as_float(o[2 * i + 1]) * inv_l);
+              w[i] = pack_bf16x2(div_by_rcp(__uint_as_float(o[2 * i]), l_i, inv_l),
+                                 div_by_rcp(__uint_as_float(o[2 * i + 1]), l_i, inv_l));
             }
             uint16_t* dst = reinterpret_cast<uint16_t*>(out) + out_off + c * 32;
 #pragma unroll
