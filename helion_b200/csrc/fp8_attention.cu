@@ -15,13 +15,14 @@
 //
 //   one warp    TMA producer: Q tile, then K/V tiles through one ring of smem slots
 //   one warp    MMA thread 1: S = Q K^T into tensor memory; tcgen05.commit publishes S and frees K slots
-//   one warp    MMA thread 2: O += P V with P read from shared memory; tcgen05.commit frees V slots
+//   one warp    MMA thread 2: O += P V with P read from shared memory (from tensor memory for head_dim 64
+//               with 128-key steps, where 64 columns are spare); tcgen05.commit frees V slots
 //               and publishes O.  (Which of warps 0-3 takes which role depends on which of the SM's
 //               CTAs this is, so that the MMA threads of co-resident CTAs sit on different schedulers.)
 //   warp 2      also allocates and frees the tensor memory
 //   warps 4-7   softmax: each thread owns one query row: pulls its 128 scores out of tensor memory
 //               into registers (which frees S for the next Q K^T at once), row max, exp2, row sum,
-//               e4m3 P into 128B-swizzled smem, rescales O in tensor memory when the max moved,
+//               e4m3 P into 128B-swizzled smem (or tensor memory), rescales O in tensor memory when the max moved,
 //               and writes the normalised output at the end of the tile
 //
 // V is accepted in both physical layouts of the reference's "[BH, D, S]" argument: D contiguous
@@ -86,6 +87,11 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   constexpr int ATT_O_COL = BN;
   constexpr int ATT_TMEM_COLS = L::TMEM_COLS;
   // P rows are BN bytes long: 128-byte or 64-byte swizzle, 8-row atoms
+  // head_dim 64 with 128-key steps leaves 64 of the 256 tensor-memory columns unused: P (128 x 128 e4m3 =
+  // 32 columns) lives there and P V reads its A operand from tensor memory -- no smem round trip, no
+  // generic-to-async proxy fence, and the P V instructions fetch only V from shared memory.
+  constexpr bool P_TMEM = D == 64 && BN == 128;
+  constexpr int ATT_P_COL = BN + D;
   constexpr uint32_t SWZ_P = (BN == 128) ? SWZ_128B : SWZ_64B;
   constexpr uint32_t SBO_P = 8 * BN;
   constexpr uint32_t SWZ_QK = (D == 128) ? SWZ_128B : SWZ_64B;  // rows of Q/K/V tiles are D bytes long
@@ -309,7 +315,11 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             for (int k = 0; k < ATT_BN / 32; ++k) {
               const uint64_t pd = desc_advance(p_desc, k * 32);
               const uint64_t vd = desc_advance(v_desc, V_KMAJOR ? k * 32 : k * 32 * D);
-              umma_f8_ss(t_o, pd, vd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+              if constexpr (P_TMEM) {
+                umma_f8_ts(t_o, tmem_base + ATT_P_COL + k * 8, vd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+              } else {
+                umma_f8_ss(t_o, pd, vd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+              }
             }
             umma_commit(&kv_empty[vs]);
             umma_commit(pv_done);
@@ -435,24 +445,36 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         if (j > 0) {
           if (__any_sync(0xffffffffu, moved)) {
+            // two 32-column groups in flight per round trip (one with four CTAs per SM: registers)
+            constexpr int GROUP = L::CTAS_PER_SM == 4 ? 1 : 2;
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-              uint32_t o[32];
-              tmem_ld_32x32b_x32(t_o + c * 32, o);
+            for (int c0 = 0; c0 < D / 32; c0 += GROUP) {
+              uint32_t o[GROUP][32];
+#pragma unroll
+              for (int c = 0; c < GROUP; ++c) tmem_ld_32x32b_x32(t_o + (c0 + c) * 32, o[c]);
               tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st_32x32b_x32(t_o + c * 32, o);
+              for (int c = 0; c < GROUP; ++c) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c][i] = __float_as_uint(__uint_as_float(o[c][i]) * alpha);
+                tmem_st_32x32b_x32(t_o + (c0 + c) * 32, o[c]);
+              }
             }
             tmem_wait_st();
           }
         }
+        if constexpr (P_TMEM) {
+          // word w of a row = keys 4w .. 4w+3 = column w of the row's lane
+          tmem_st_32x32b_x32(tmem_base + ATT_P_COL + lane_sel, packed);
+          tmem_wait_st();
+        } else {
 #pragma unroll
-        for (int ch = 0; ch < BN / 16; ++ch) {
-          *reinterpret_cast<uint4*>(p_row + ((static_cast<uint32_t>(ch) ^ p_xor) << 4)) =
-              make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
+          for (int ch = 0; ch < BN / 16; ++ch) {
+            *reinterpret_cast<uint4*>(p_row + ((static_cast<uint32_t>(ch) ^ p_xor) << 4)) =
+                make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
+          }
+          fence_proxy_async_smem();
         }
-        fence_proxy_async_smem();
         tc_fence_before_sync();
         mbar_arrive(p_full);
         m_i = m_new;
