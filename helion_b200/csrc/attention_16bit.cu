@@ -11,8 +11,10 @@
 // producer warp, one MMA thread for S = Q K^T and one for O += P V (kind::f16 instructions), four
 // softmax warps with one query row per thread, tiles handed out through the shared-memory tile
 // queue.  What differs is the geometry: rows are 2*D bytes long, so a Q / K / V tile is stored as one
-// or two column blocks of 128-byte rows (head_dim 64 / 128), keys are walked in steps of 64, and P is
-// written as 16-bit values (one 128-byte row per query).
+// or two column blocks of 128-byte rows (head_dim 64 / 128), keys are walked in steps of 128 (head_dim
+// 64) or 64 (head_dim 128), and P, as 16-bit values, never touches shared memory: it is written to the
+// tensor-memory columns that S and O leave free (S: BN, O: D, P: BN/2 of the 256 columns) and P V reads
+// its A operand from there.
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
@@ -25,22 +27,24 @@ namespace hb {
 namespace {
 
 constexpr int A16_BM = 128;  // query rows per tile
-constexpr int A16_BN = 64;   // keys per step: one 128-byte row of 16-bit P per query
 constexpr int A16_THREADS = 256;
 constexpr int A16_SOFTMAX_THREADS = 128;
 
 template <int D>
 struct Attn16Layout {
+  static constexpr int BN = D == 64 ? 128 : 64;        // keys per step
   static constexpr int ROW_BYTES = D * 2;
   static constexpr int BLOCKS = ROW_BYTES / 128;       // 128-byte column blocks per row
   static constexpr int Q_BYTES = A16_BM * ROW_BYTES;   // BLOCKS x [128 rows x 128 B]
-  static constexpr int TILE_BYTES = A16_BN * ROW_BYTES;  // one K or V tile: BLOCKS x [64 rows x 128 B]
-  static constexpr int P_BYTES = A16_BM * 128;
-  static constexpr int KV_STAGES = D == 64 ? 8 : 3;
-  static constexpr int TMEM_COLS = (A16_BN + D <= 128) ? 128 : 256;  // S in [0,64), O in [64, 64 + D)
+  static constexpr int TILE_BYTES = BN * ROW_BYTES;    // one K or V tile: BLOCKS x [BN rows x 128 B], 16 KB
+  static constexpr int KV_STAGES = D == 64 ? 5 : 4;
+  // tensor memory: S in [0, BN), O in [BN, BN + D), P (two values per column) in [BN + D, BN + D + BN/2)
+  static constexpr int O_COL = BN;
+  static constexpr int P_COL = BN + D;
+  static constexpr int TMEM_COLS = 256;
+  static_assert(P_COL + BN / 2 <= TMEM_COLS, "S, O and P must fit the CTA's tensor memory");
   static constexpr int Q_OFFSET = 0;
-  static constexpr int P_OFFSET = Q_BYTES;
-  static constexpr int KV_OFFSET = P_OFFSET + P_BYTES;
+  static constexpr int KV_OFFSET = Q_BYTES;
   static constexpr int BAR_OFFSET = KV_OFFSET + KV_STAGES * TILE_BYTES;
   // q_full q_empty s_full s_free p_full pv_done drain drain_pv kv_full[ST] kv_empty[ST]
   static constexpr int NUM_BARS = 8 + 2 * KV_STAGES;
@@ -77,6 +81,7 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   using L = Attn16Layout<D>;
   constexpr int ST = L::KV_STAGES;
   constexpr int NB = L::BLOCKS;
+  constexpr int A16_BN = L::BN;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -242,10 +247,9 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       // ------------------------------- MMA thread 2: O (+)= P V ------------------------------
       if (lane == 0) {
         constexpr uint32_t idesc_pv = make_idesc<KIND>(A16_BM, D, false, true);
-        const uint32_t p_addr = smem_u32(smem + L::P_OFFSET);
         const uint32_t kv_addr = smem_u32(smem + L::KV_OFFSET);
-        const uint32_t t_o = tmem_base + A16_BN;
-        const uint64_t p_desc = make_smem_desc(p_addr, 16, 1024, SWZ_128B);
+        const uint32_t t_o = tmem_base + L::O_COL;
+        const uint32_t t_p = tmem_base + L::P_COL;
         uint32_t g = 0;
         uint32_t slot_it = 0;
         uint32_t tile_iter = 0;
@@ -266,13 +270,13 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
               break;
             }
             tc_fence_after_sync();
-            // V [64 keys, D] with D contiguous: MN-major B; column blocks of 64 elements (128 B) lie
-            // 64 x 128 bytes apart, 8 key rows per atom (1024 B), 16 keys (2048 B) per instruction
+            // V [BN keys, D] with D contiguous: MN-major B; column blocks of 64 elements (128 B) lie
+            // BN x 128 bytes apart, 8 key rows per atom (1024 B), 16 keys (2048 B) per instruction.
+            // A = P from tensor memory: 16 keys = 8 columns per instruction.
             const uint64_t v_desc = make_smem_desc(kv_addr + vs * L::TILE_BYTES, A16_BN * 128, 1024, SWZ_128B);
 #pragma unroll
             for (int k = 0; k < A16_BN / 16; ++k) {
-              umma_f16_ss(t_o, desc_advance(p_desc, k * 32), desc_advance(v_desc, k * 16 * 128), idesc_pv,
-                          (j | k) != 0 ? 1u : 0u);
+              umma_f16_ts(t_o, t_p + k * 8, desc_advance(v_desc, k * 16 * 128), idesc_pv, (j | k) != 0 ? 1u : 0u);
             }
             umma_commit(&kv_empty[vs]);
             umma_commit(pv_done);
@@ -292,10 +296,9 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t t_s = tmem_base + lane_sel;
-    const uint32_t t_o = tmem_base + A16_BN + lane_sel;
-    // P row of this thread: 128 bytes, 16-byte chunks XOR-swizzled with (row % 8)
-    uint8_t* p_row = smem + L::P_OFFSET + row_in_tile * 128;
-    const uint32_t p_xor = static_cast<uint32_t>(row_in_tile & 7);
+    const uint32_t t_o = tmem_base + L::O_COL + lane_sel;
+    const uint32_t t_p = tmem_base + L::P_COL + lane_sel;
+    constexpr int NC = A16_BN / 32;  // 32-column chunks of the score row
     uint32_t g = 0;
     bool ok = true;
 
@@ -315,9 +318,9 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        uint32_t s[2][32];
-        tmem_ld_32x32b_x32(t_s, s[0]);
-        tmem_ld_32x32b_x32(t_s + 32, s[1]);
+        uint32_t s[NC][32];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) tmem_ld_32x32b_x32(t_s + c * 32, s[c]);
         tmem_wait_ld();
         tc_fence_before_sync();
         mbar_arrive(s_free);
@@ -327,7 +330,7 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         const int valid = Sk - j * A16_BN;
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;  // independent chains
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < NC; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             float t0 = __uint_as_float(s[c][i]), t1 = __uint_as_float(s[c][i + 1]);
@@ -360,16 +363,16 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         const bool moved = m_new > m_i;
         const float alpha = fast_exp2(m_i - m_new);
         float sum0 = 0.0f, sum1 = 0.0f;
-        uint32_t packed[32];
+        uint32_t packed[NC][16];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < NC; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const float p0 = fast_exp2(__uint_as_float(s[c][i]) - m_new);
             const float p1 = fast_exp2(__uint_as_float(s[c][i + 1]) - m_new);
             sum0 += p0;
             sum1 += p1;
-            packed[c * 16 + i / 2] = pack16x2<KIND>(p0, p1);
+            packed[c][i / 2] = pack16x2<KIND>(p0, p1);
           }
         }
         l_i = l_i * alpha + (sum0 + sum1);
@@ -382,22 +385,23 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
         if (j > 0 && __any_sync(0xffffffffu, moved)) {
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32b_x32(t_o + c * 32, o);
+          for (int c0 = 0; c0 < D / 32; c0 += 2) {  // two 32-column groups per round trip
+            uint32_t o[2][32];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tmem_ld_32x32b_x32(t_o + (c0 + c) * 32, o[c]);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x32b_x32(t_o + c * 32, o);
-          }
-          tmem_wait_st();
-        }
+            for (int c = 0; c < 2; ++c) {
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          *reinterpret_cast<uint4*>(p_row + ((static_cast<uint32_t>(ch) ^ p_xor) << 4)) =
-              make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
+              for (int i = 0; i < 32; ++i) o[c][i] = __float_as_uint(__uint_as_float(o[c][i]) * alpha);
+              tmem_st_32x32b_x32(t_o + (c0 + c) * 32, o[c]);
+            }
+          }
         }
-        fence_proxy_async_smem();
+        // P: column w of this row's lane = keys 2w (low half) and 2w + 1
+#pragma unroll
+        for (int c = 0; c < NC; ++c) tmem_st_32x32b_x16(t_p + c * 16, packed[c]);
+        tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(p_full);
         m_i = m_new;
@@ -494,7 +498,7 @@ int launch_attention_16bit(const AttnArgs& a, DeviceCtx* ctx) {
   CUtensorMap tq, tk, tv;
   // maps over bytes: 128-byte column blocks of rows that are 2*D bytes long
   const uint32_t qbox[3] = {128, A16_BM, 1};
-  const uint32_t kvbox[3] = {128, A16_BN, 1};
+  const uint32_t kvbox[3] = {128, static_cast<uint32_t>(a.D == 64 ? Attn16Layout<64>::BN : Attn16Layout<128>::BN), 1};
   const uint64_t qdims[3] = {static_cast<uint64_t>(a.D * 2), static_cast<uint64_t>(a.S), static_cast<uint64_t>(a.BH)};
   const uint64_t kdims[3] = {static_cast<uint64_t>(a.D * 2), static_cast<uint64_t>(a.Sk), static_cast<uint64_t>(a.BH)};
   const uint64_t qs[2] = {static_cast<uint64_t>(a.q_strides[1] * 2), static_cast<uint64_t>(a.q_strides[0] * 2)};

@@ -1058,9 +1058,10 @@ size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int 
 // Chooses the table row with the smallest estimated time of the persistent schedule, in SM cycles:
 //   waves x (K blocks x cycles per K block / measured tensor-pipe efficiency + exposed epilogue).
 // Efficiencies are tensor-pipe-active fractions measured at 8192^3 on B200: single-CTA 128x256 0.75,
-// 128x128 0.51, 128x64 0.26; CTA pair 256x256 (staged TMA-store epilogue, hidden behind the next
-// tile) 0.85; CTA pair 512x256 0.93 in the main loop but its epilogue (~4500 cycles) is exposed because
-// its two accumulators fill tensor memory -- so it wins for long K only.  A pair tile occupies two SMs.
+// 128x128 0.51, 128x64 0.26.  The two CTA-pair rows are fitted to the sweep (python -m helion_b200.sweep)
+// over K = 4096 and K = 8192 problems: time per round of tiles = a * K blocks + b with the same main-loop
+// efficiency (0.88) and ~3000 cycles per tile that no overlap hides, for 256x256 and 512x256 tiles
+// alike -- so the larger tile wins whenever it does not cost an extra round.  A pair tile occupies two SMs.
 static int gemm_select_config_nosplit(int64_t M, int64_t N, int64_t K, bool y_colmajor, int num_sms) {
   struct Candidate {
     int cfg;
@@ -1072,8 +1073,8 @@ static int gemm_select_config_nosplit(int64_t M, int64_t N, int64_t K, bool y_co
   };
   const Candidate candidates[5] = {
       {3, 128, 256, false, 512.0, 0.75, 0.0},  {1, 128, 128, false, 256.0, 0.51, 0.0},
-      {2, 128, 64, false, 128.0, 0.26, 0.0},   {6, 256, 256, true, 512.0, 0.85, 0.0},
-      {14, 512, 256, true, 1024.0, 0.93, 4500.0},
+      {2, 128, 64, false, 128.0, 0.26, 0.0},   {6, 256, 256, true, 512.0, 0.88, 3000.0},
+      {14, 512, 256, true, 1024.0, 0.88, 3300.0},
   };
   const double k_blocks = static_cast<double>((K + BK - 1) / BK);
   int best = 3;

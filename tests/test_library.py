@@ -141,3 +141,15 @@ def test_ops_check_dtypes_and_shapes_like_the_reference():
     v = torch.zeros(2, 64, 16).to(torch.float8_e4m3fn)
     with pytest.raises(ValueError, match="batch\\*heads"):
         hb.fp8_attention(q, q, v, 3, 2)
+
+
+def test_sweep_tool_needs_a_gpu_and_knows_the_benchmark_shapes():
+    """The table sweep is a GPU tool: without a device it says so and exits 2 (no CPU path)."""
+    import torch
+
+    from helion_b200 import sweep
+
+    assert (8192, 8192, 8192) in sweep.GEMM_SHAPES and (16, 14336, 4096) in sweep.GEMM_SHAPES
+    assert (4, 48, 1024, 64) in sweep.ATTN_SHAPES and (8, 32, 4096, 128) in sweep.ATTN_SHAPES
+    if not torch.cuda.is_available():
+        assert sweep.main(["--op", "gemm"]) == 2
