@@ -325,55 +325,66 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tc_fence_before_sync();
         mbar_arrive(s_free);
 
-        // t = cast16(cast16(qk) * c): the two 16-bit roundings of the reference's tensors; keys beyond
-        // seq_k count as -inf
+        // keys beyond seq_k count as -inf (ragged last step only; -inf survives the roundings and the scale)
         const int valid = Sk - j * A16_BN;
+        if (valid < A16_BN) {
+#pragma unroll
+          for (int c = 0; c < NC; ++c) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (c * 32 + i >= valid) s[c][i] = __float_as_uint(-INFINITY);
+            }
+          }
+        }
+        // t = cast16(cast16(qk) * c): the two 16-bit roundings of the reference's tensors, on packed pairs
+        const uint64_t c2 = pack2f(scale_log2, scale_log2);
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;  // independent chains
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            float t0 = __uint_as_float(s[c][i]), t1 = __uint_as_float(s[c][i + 1]);
-            float t2 = __uint_as_float(s[c][i + 2]), t3 = __uint_as_float(s[c][i + 3]);
-            round16_pair<KIND>(t0, t1);
-            round16_pair<KIND>(t2, t3);
-            t0 *= scale_log2;
-            t1 *= scale_log2;
-            t2 *= scale_log2;
-            t3 *= scale_log2;
-            round16_pair<KIND>(t0, t1);
-            round16_pair<KIND>(t2, t3);
-            if (valid < A16_BN) {  // ragged last step only
-              if (c * 32 + i >= valid) t0 = -INFINITY;
-              if (c * 32 + i + 1 >= valid) t1 = -INFINITY;
-              if (c * 32 + i + 2 >= valid) t2 = -INFINITY;
-              if (c * 32 + i + 3 >= valid) t3 = -INFINITY;
+          for (int i = 0; i < 32; i += 8) {
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              float t0 = __uint_as_float(s[c][i + 2 * h]), t1 = __uint_as_float(s[c][i + 2 * h + 1]);
+              round16_pair<KIND>(t0, t1);
+              uint32_t u0, u1;
+              unpack2(fmul2(pack2f(t0, t1), c2), u0, u1);
+              t0 = __uint_as_float(u0);
+              t1 = __uint_as_float(u1);
+              round16_pair<KIND>(t0, t1);
+              s[c][i + 2 * h] = __float_as_uint(t0);
+              s[c][i + 2 * h + 1] = __float_as_uint(t1);
+              if (h == 0) mx0 = fmax3(mx0, t0, t1);
+              if (h == 1) mx1 = fmax3(mx1, t0, t1);
+              if (h == 2) mx2 = fmax3(mx2, t0, t1);
+              if (h == 3) mx3 = fmax3(mx3, t0, t1);
             }
-            s[c][i] = __float_as_uint(t0);
-            s[c][i + 1] = __float_as_uint(t1);
-            s[c][i + 2] = __float_as_uint(t2);
-            s[c][i + 3] = __float_as_uint(t3);
-            mx0 = fmaxf(mx0, t0);
-            mx1 = fmaxf(mx1, t1);
-            mx2 = fmaxf(mx2, t2);
-            mx3 = fmaxf(mx3, t3);
           }
         }
         const float m_new = fmaxf(m_i, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
         const bool moved = m_new > m_i;
         const float alpha = fast_exp2(m_i - m_new);
-        float sum0 = 0.0f, sum1 = 0.0f;
+        // p = exp2(t - m) on packed pairs; the even and the odd keys are summed separately, as before
+        const uint64_t negm2 = pack2f(-m_new, -m_new);
+        uint64_t sum2 = 0ull;  // (0.0f, 0.0f)
         uint32_t packed[NC][16];
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(__uint_as_float(s[c][i]) - m_new);
-            const float p1 = fast_exp2(__uint_as_float(s[c][i + 1]) - m_new);
-            sum0 += p0;
-            sum1 += p1;
-            packed[c][i / 2] = pack16x2<KIND>(p0, p1);
+            const uint64_t p2 = exp2_pair_mufu(fadd2(pack2(s[c][i], s[c][i + 1]), negm2));
+            sum2 = fadd2(sum2, p2);
+            uint32_t p0, p1;
+            unpack2(p2, p0, p1);
+            packed[c][i / 2] = pack16x2<KIND>(__uint_as_float(p0), __uint_as_float(p1));
           }
+        }
+        float sum0, sum1;
+        {
+          uint32_t u0, u1;
+          unpack2(sum2, u0, u1);
+          sum0 = __uint_as_float(u0);
+          sum1 = __uint_as_float(u1);
         }
         l_i = l_i * alpha + (sum0 + sum1);
 
