@@ -469,7 +469,6 @@ static int fp8_attention_impl(const void* q, const void* k, const void* v, void*
   if (BH < 1 || S < 1 || BH > INT32_MAX || S > INT32_MAX) {
     return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: batch*heads and seq must be in [1, 2^31)");
   }
-  if (S % 16 != 0 || Sk % 16 != 0) return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: seq must be a multiple of 16");
   if (Sk < 1 || Sk > INT32_MAX) return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: seq_k must be in [1, 2^31)");
   if (causal != 0 && Sk < S) {
     return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: the causal mask needs seq_k >= seq_q (every query must see a key)");

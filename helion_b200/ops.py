@@ -39,6 +39,44 @@ def _stream_ptr(device_index: int) -> int:
     return torch.cuda.current_stream(device_index).cuda_stream
 
 
+def _round_up(v: int, mult: int) -> int:
+    return (v + mult - 1) // mult * mult
+
+
+def _pad_gemm_operands(x: torch.Tensor, y: torch.Tensor, kp: int, np_: int):
+    """Zero-padded copies of ``x [M,K]`` -> ``[M,kp]`` and ``y [K,N]`` -> ``[kp,np_]`` (y keeps its layout).
+
+    The C ABI takes TMA-legal operands only (16-byte aligned rows); the reference accepts any M, N, K
+    (masked tiles, helion/_compiler/inductor_lowering.py:825-831).  Zero rows / columns add nothing to
+    the products, so the odd shapes go through the same kernels on padded device copies and the
+    caller gets the ``[:, :N]`` part back.
+    """
+    m, k = x.shape
+    n = y.shape[1]
+    if kp != k:
+        xp = x.new_zeros((m, kp))
+        xp[:, :k].copy_(x)
+        x = xp
+    if kp != k or np_ != n:
+        if y.stride(0) == 1 and y.stride(1) != 1:  # column-major: pad the [N, K] storage
+            yt = y.new_zeros((np_, kp))
+            yt[:n, :k].copy_(y.t())
+            y = yt.t()
+        else:
+            yp = y.new_zeros((kp, np_))
+            yp[:k, :n].copy_(y)
+            y = yp
+    return x, y
+
+
+def _pad_vector(v: Optional[torch.Tensor], n: int, np_: int, fill: float) -> Optional[torch.Tensor]:
+    if v is None or v.numel() != n or np_ == n:
+        return v
+    out = v.new_full((np_,), fill)
+    out[:n].copy_(v.reshape(n))
+    return out
+
+
 def fp8_gemm(
     x: torch.Tensor,
     y: torch.Tensor,
@@ -84,6 +122,17 @@ def fp8_gemm(
         return out
     if k == 0:
         return out.zero_()
+    kp, np_ = _round_up(k, 16), _round_up(n, 16)
+    if kp != k or np_ != n:  # odd K or N: same kernels on zero-padded copies (see _pad_gemm_operands)
+        xp, yp = _pad_gemm_operands(x, y, kp, np_)
+        if scale_b is not None and scale_b.numel() != 1:
+            _check_scales(scale_a, scale_b, m, n, x.device)
+            scale_b = _pad_vector(scale_b, n, np_, 1.0)
+        res = fp8_gemm(xp, yp, out_dtype=out_dtype, config=config, scale_a=scale_a, scale_b=scale_b)
+        out.copy_(res[:, :n])
+        return out
+    if x.stride(0) % 16 != 0:
+        x = x.contiguous()
     lib = _lib.load()
     cfg = -1 if config is None else int(config)
     # Split-K rows of the tile table need scratch for their fp32 partial sums; like `out` it comes
@@ -173,6 +222,10 @@ def fp8_attention(
         k = k.contiguous()
     if v.stride(1) != 1 and v.stride(2) != 1:
         v = v.contiguous()
+    if v.stride(2) == 1 and v.stride(1) != 1 and (v.stride(1) % 16 != 0 or v.stride(0) % 16 != 0):
+        # keys contiguous with rows that are not 16-byte aligned (seq_k % 16 != 0): take the other
+        # physical layout of the same logical tensor (head_dim contiguous), which any seq_k fits
+        v = v.transpose(1, 2).contiguous().transpose(1, 2)
     if out is None:
         out = torch.empty((batch, heads, s, d), dtype=out_dtype, device=q.device)
     elif out.dtype != out_dtype or tuple(out.shape) != (batch, heads, s, d) or not out.is_contiguous():
@@ -313,6 +366,14 @@ def matmul(
         if bias32 is not None:
             out += bias32.to(out_dtype)
         return out.relu_() if relu else out
+    kp, np_ = _round_up(k, 8), _round_up(n, 8)
+    if kp != k or np_ != n:  # odd K or N: same kernels on zero-padded copies (see _pad_gemm_operands)
+        xp, yp = _pad_gemm_operands(x, y, kp, np_)
+        res = matmul(xp, yp, bias=_pad_vector(bias32, n, np_, 0.0), relu=relu, out_dtype=out_dtype, config=config)
+        out.copy_(res[:, :n])
+        return out
+    if x.stride(0) % 8 != 0:
+        x = x.contiguous()
     code = _lib.load().hb200_gemm_16bit(
         x.data_ptr(), y.data_ptr(), out.data_ptr(), m, n, k,
         x.stride(0), x.stride(1), y.stride(0), y.stride(1), out.stride(0),

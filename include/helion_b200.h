@@ -122,7 +122,8 @@ HB200_API int hb200_fp8_gemm_select_config(int64_t M, int64_t N, int64_t K, int 
  *      preprocess_fp8_attention_inputs really produces, examples/fp8_attention.py:127-132) and
  *      stride_s == 1 (a genuinely contiguous [BH, D, S]).
  *   out: [BH, S, D] with strides {bh, s, d}, d stride 1; FP8 (reference), or BF16 / FP32.
- *   D in {64, 128}; S >= 1 with S % 16 == 0; scale_log2 = log2(e)/sqrt(D) for the reference's
+ *   D in {64, 128}; any S >= 1 (every stride except the unit one a multiple of 16 bytes, so a
+ *   [BH, D, S] tensor with S contiguous needs S % 16 == 0); scale_log2 = log2(e)/sqrt(D) for the reference's
  *   scale (examples/fp8_attention.py:50-52).
  */
 HB200_API int hb200_fp8_attention(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S, int64_t D,
@@ -157,7 +158,7 @@ HB200_API int hb200_fp8_attention_ws(const void* q, const void* k, const void* v
  * A hidden score counts as -inf before the row max, like the padding of a ragged key tile; tiles skip
  * the key steps none of their rows can see and are handed out longest first.
  *   q [BH, S_q, D], k [BH, S_k, D], v logical [BH, D, S_k], out [BH, S_q, D]; strides as for
- *   hb200_fp8_attention; S_q % 16 == 0, S_k % 16 == 0.
+ *   hb200_fp8_attention.
  *   workspace: NULL (fixed tile order) or HB200_ATTN_WORKSPACE_BYTES as for hb200_fp8_attention_ws
  *   (recommended with a mask: the tiles of a slice differ in length). */
 HB200_API int hb200_fp8_attention_ex(const void* q, const void* k, const void* v, void* out, int64_t BH, int64_t S_q,

@@ -287,10 +287,26 @@ def test_unsupported_shapes_raise(hb):
     v = torch.zeros(2, 96, 128, device="cuda").to(torch.float8_e4m3fn)
     with pytest.raises(ValueError, match="head_dim must be 64 or 128"):
         hb.fp8_attention(q, q, v, 1, 2)
-    q = torch.zeros(2, 100, 64, device="cuda").to(torch.float8_e4m3fn)
-    v = torch.zeros(2, 64, 100, device="cuda").to(torch.float8_e4m3fn)
-    with pytest.raises(ValueError, match="multiple of 16"):
-        hb.fp8_attention(q, q, v, 1, 2)
+
+
+@pytest.mark.parametrize("s,sk,d,causal", [(100, 100, 64, False), (72, 200, 128, False), (36, 77, 64, True), (129, 129, 128, True)])
+def test_sequence_lengths_that_are_not_multiples_of_16(hb, s, sk, d, causal):
+    """Any sequence length, like the reference (masked tiles): ragged query rows are not stored, ragged
+    keys count as -inf, and a key-contiguous v with unaligned rows is re-laid out by the wrapper."""
+    g = torch.Generator().manual_seed(s * 1000 + sk)
+    bh = 3
+    q8 = torch.randn(bh, s, d, generator=g).to(torch.float8_e4m3fn)
+    k8 = torch.randn(bh, sk, d, generator=g).to(torch.float8_e4m3fn)
+    v8 = torch.randn(bh, sk, d, generator=g).to(torch.float8_e4m3fn)
+    blk8, blk_raw = o.fp8_attention(bits(q8), bits(k8), bits(v8.permute(0, 2, 1)), 1, bh, return_parts=True,
+                                    block_n=128, causal=causal)
+    for v_dev in (v8.cuda().permute(0, 2, 1), v8.cuda().permute(0, 2, 1).contiguous()):  # D- and key-contiguous
+        got = hb.fp8_attention(q8.cuda(), k8.cuda(), v_dev, 1, bh, out_dtype=torch.float32, causal=causal)
+        got8 = hb.fp8_attention(q8.cuda(), k8.cuda(), v_dev, 1, bh, causal=causal)
+        assert tuple(got.shape) == (1, bh, s, d) and torch.isfinite(got).all()
+        assert_near_bit_exact(got.cpu().numpy(), bits(got8), blk_raw, blk8)
+    torch.cuda.synchronize()
+    _lib.check_status(0)
 
 
 class TestFullSize:

@@ -77,7 +77,8 @@ def test_attention_argument_validation_needs_no_gpu(built_library):
 
     assert call(D=96) == _lib.ERR_BAD_SHAPE
     assert "head_dim" in _lib.last_error()
-    assert call(S=100) == _lib.ERR_BAD_SHAPE
+    assert call(S=0) == _lib.ERR_BAD_SHAPE
+    assert call(S=100, v=(6400, 100, 1)) == _lib.ERR_BAD_STRIDE  # key-contiguous v with unaligned rows
     assert call(dt=_lib.DT_FP16) == _lib.ERR_BAD_DTYPE
     assert call(q=(8192, 1, 128)) == _lib.ERR_BAD_STRIDE
     assert call(v=(8192, 2, 128)) == _lib.ERR_BAD_STRIDE

@@ -120,8 +120,6 @@ def test_argument_checks(hb):
         hb.matmul(x, x.bfloat16())
     with pytest.raises(TypeError, match="out_dtype"):
         hb.matmul(x, x, out_dtype=torch.bfloat16)
-    with pytest.raises(ValueError, match="multiple of 8"):
-        hb.matmul(x[:, :60].contiguous(), x[:60])
     with pytest.raises(ValueError, match="bias must be a vector"):
         hb.matmul(x, x, bias=torch.zeros(8, device="cuda"))
 
@@ -150,3 +148,20 @@ class TestFullSize:
         perm = torch.randperm(8192, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
         assert torch.equal(hb.matmul(x[perm], y), out[perm])
         assert torch.equal(hb.matmul(x * 2, y, out_dtype=torch.float32), hb.matmul(x, y, out_dtype=torch.float32) * 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(64, 64, 60), (33, 50, 17), (130, 257, 129)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_shapes_that_are_not_multiples_of_8(hb, m, n, k, dtype):
+    """Any M, N, K like the reference: odd K / N run on zero-padded device copies; bias and ReLU ride along."""
+    g = torch.Generator().manual_seed(m * n + k)
+    x, y, b = torch.randn(m, k, generator=g).to(dtype), torch.randn(k, n, generator=g).to(dtype), torch.randn(n, generator=g).to(dtype)
+    name = "fp16" if dtype == torch.float16 else "bf16"
+    for yd in (y.cuda(), y.t().contiguous().cuda().t()):
+        got = hb.matmul(x.cuda(), yd, bias=b.cuda(), relu=True)
+        assert tuple(got.shape) == (m, n) and got.dtype == dtype and got.is_contiguous()
+        want = o.matmul_16bit(x.float().numpy(), y.float().numpy(), b.float().numpy(), True, name)
+        np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=2e-2, atol=2e-2)
+    torch.cuda.synchronize()
+    _lib.check_status(0)
