@@ -176,6 +176,19 @@ def _check_scales(scale_a, scale_b, m: int, n: int, device):
     )
 
 
+def _kernel_head_dim(d: int, what: str) -> int:
+    """The head_dim the kernels run a logical head_dim at: 64 or 128 (zero-padded columns in between)."""
+    if d < 1 or d > 128:
+        raise ValueError(f"{what}: head_dim must be in [1, 128] (kernels exist for 64 and 128; smaller ones are zero-padded), got {d}")
+    return 64 if d <= 64 else 128
+
+
+def _pad_last(t: torch.Tensor, dp: int) -> torch.Tensor:
+    out = t.new_zeros((*t.shape[:-1], dp))
+    out[..., : t.shape[-1]].copy_(t)
+    return out
+
+
 def fp8_attention(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -216,6 +229,21 @@ def fp8_attention(
     if out_dtype not in (torch.float8_e4m3fn, torch.bfloat16, torch.float32):
         raise TypeError(f"fp8_attention out_dtype must be float8_e4m3fn, bfloat16 or float32, got {out_dtype}")
     dev = _require_cuda(q, k, v)
+    dp = _kernel_head_dim(d, "fp8_attention")
+    if dp != d and bh > 0 and s > 0:
+        # The kernels exist for head_dim 64 and 128; the reference pads any head_dim to a power of two
+        # and masks (examples/fp8_attention.py:31-33).  Zero columns add nothing to q k^T and give
+        # zero output columns, so the same kernel runs on padded copies with the scale of the real D.
+        qp, kp = (_pad_last(t, dp) for t in (q, k))
+        vp = _pad_last(v.transpose(1, 2), dp).transpose(1, 2)
+        res = torch.empty((batch, heads, s, dp), dtype=out_dtype, device=q.device)
+        attention_into(qp, kp, vp, res.view(bh, s, dp), config=config, balanced=balanced, causal=causal, head_dim=d)
+        if out is None:
+            return res[..., :d].contiguous()
+        if out.dtype != out_dtype or tuple(out.shape) != (batch, heads, s, d):
+            raise ValueError("fp8_attention: `out` must be a [batch, heads, seq, dim] tensor of out_dtype")
+        out.copy_(res[..., :d])
+        return out
     if q.stride(2) != 1:
         q = q.contiguous()
     if k.stride(2) != 1:
@@ -238,7 +266,7 @@ def fp8_attention(
 
 def attention_into(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out3: torch.Tensor, *, config: Optional[int] = None,
-    balanced: Optional[bool] = None, causal: bool = False,
+    balanced: Optional[bool] = None, causal: bool = False, head_dim: Optional[int] = None,
 ) -> None:
     """Launch the attention kernel on ``[BH,S,D]`` / ``[BH,D,S]`` tensors, writing ``out3 [BH,S,D]``.
 
@@ -254,8 +282,9 @@ def attention_into(
     """
     bh, s, d = q.shape
     dev = _require_cuda(q, k, v, out3)
-    # The kernel scales by log2(e)/sqrt(D) and uses exp2, like examples/fp8_attention.py:50-52.
-    scale_log2 = (1.0 / math.sqrt(float(d))) * 1.44269504
+    # The kernel scales by log2(e)/sqrt(D) and uses exp2, like examples/fp8_attention.py:50-52
+    # (head_dim: the logical D when the tensors carry zero-padded columns).
+    scale_log2 = (1.0 / math.sqrt(float(d if head_dim is None else head_dim))) * 1.44269504
     arr = ctypes.c_int64 * 3
     lib = _lib.load()
     cfg = -1 if config is None else int(config)
@@ -413,14 +442,17 @@ def attention(
         raise TypeError(f"attention out_dtype must be {q_in.dtype} or float32, got {out_dtype}")
     dev = _require_cuda(q_in, k_in, v_in)
     q, k, v = (t.reshape(-1, t.shape[-2], d) for t in (q_in, k_in, v_in))
-    q, k, v = (t if t.stride(2) == 1 else t.contiguous() for t in (q, k, v))
     bh = q.shape[0]
-    out = torch.empty((bh, m_dim, d), dtype=out_dtype, device=q.device)
     if bh == 0 or m_dim == 0:
-        return out.view(q_in.shape)
+        return torch.empty(q_in.shape, dtype=out_dtype, device=q_in.device)
     if n_dim == 0:
         raise ValueError("attention: k and v hold no keys")
     scale_log2 = (1.0 / math.sqrt(float(d))) * 1.44269504  # qk_scale of examples/attention.py:60-61
+    d_logical, d = d, _kernel_head_dim(d, "attention")
+    if d != d_logical:  # zero-padded columns, the scale of the real head_dim (see fp8_attention)
+        q, k, v = (_pad_last(t, d) for t in (q, k, v))
+    q, k, v = (t if t.stride(2) == 1 and t.stride(1) % 8 == 0 and t.stride(0) % 8 == 0 else t.contiguous() for t in (q, k, v))
+    out = torch.empty((bh, m_dim, d), dtype=out_dtype, device=q.device)
     if balanced is None:
         balanced = n_dim >= 2048
     ws = torch.empty(_lib.ATTN_WORKSPACE_BYTES, dtype=torch.uint8, device=q.device) if balanced else None
@@ -432,4 +464,6 @@ def attention(
         ws.numel() if ws is not None else 0, dev, _stream_ptr(dev),
     )
     _lib.raise_for(code, "attention")
+    if d != d_logical:
+        out = out[..., :d_logical].contiguous()
     return out.view(q_in.shape)

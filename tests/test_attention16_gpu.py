@@ -33,7 +33,8 @@ def hb(built_library):
 @pytest.mark.parametrize(
     "lead,sq,sk,dim",
     [((1, 2), 128, 128, 64), ((2, 4), 256, 256, 64), ((1, 2), 512, 512, 128), ((3,), 80, 208, 64), ((1, 1), 16, 16, 128),
-     ((2, 2), 1024, 1040, 64), ((1, 3), 200, 72, 128), ((5, 7), 144, 144, 64), ((), 192, 320, 128)],
+     ((2, 2), 1024, 1040, 64), ((1, 3), 200, 72, 128), ((5, 7), 144, 144, 64), ((), 192, 320, 128),
+     ((2, 2), 100, 77, 32), ((3,), 256, 130, 96), ((1, 2), 64, 64, 80)],  # head_dims in between: zero-padded columns
 )
 def test_matches_oracle(hb, lead, sq, sk, dim, dtype):
     g = torch.Generator().manual_seed(sq + sk + dim)
@@ -42,7 +43,8 @@ def test_matches_oracle(hb, lead, sq, sk, dim, dtype):
     v = torch.randn(*lead, sk, dim, generator=g).to(dtype)
     f3 = lambda t: t.float().reshape(-1, t.shape[-2], dim).numpy()  # noqa: E731
     one, one_raw = o.attention_16bit(f3(q), f3(k), f3(v), NAME[dtype], return_parts=True)
-    blk, blk_raw = o.attention_16bit(f3(q), f3(k), f3(v), NAME[dtype], block_n=64, return_parts=True)
+    # the kernel walks 128 keys per step at (padded) head_dim 64 and 64 at head_dim 128
+    blk, blk_raw = o.attention_16bit(f3(q), f3(k), f3(v), NAME[dtype], block_n=128 if dim <= 64 else 64, return_parts=True)
     out = hb.attention(q.cuda(), k.cuda(), v.cuda())
     out32 = hb.attention(q.cuda(), k.cuda(), v.cuda(), out_dtype=torch.float32)
     assert out.dtype == dtype and out.shape == q.shape and out32.shape == q.shape
@@ -68,8 +70,9 @@ def test_example_module_and_argument_checks(hb):
     assert torch.equal(mod.attention_dynamic(q, q, q), mod.attention(q, q, q))
     with pytest.raises(TypeError, match="float16 or three bfloat16"):
         mod.attention(q.float(), q.float(), q.float())  # the reference's fp32 default is not built
-    with pytest.raises(ValueError, match="head_dim must be 64 or 128"):
-        hb.attention(q[..., :32].contiguous(), q[..., :32].contiguous(), q[..., :32].contiguous())
+    wide = torch.zeros(2, 128, 256, device="cuda", dtype=torch.float16)
+    with pytest.raises(ValueError, match=r"head_dim must be in \[1, 128\]"):
+        hb.attention(wide, wide, wide)
     with pytest.raises(AssertionError):
         hb.attention(q, q[:, :, :64], q)
 

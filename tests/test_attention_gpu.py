@@ -283,10 +283,27 @@ def test_example_module_entry_points(hb):
 
 
 def test_unsupported_shapes_raise(hb):
-    q = torch.zeros(2, 128, 96, device="cuda").to(torch.float8_e4m3fn)
-    v = torch.zeros(2, 96, 128, device="cuda").to(torch.float8_e4m3fn)
-    with pytest.raises(ValueError, match="head_dim must be 64 or 128"):
+    q = torch.zeros(2, 128, 256, device="cuda").to(torch.float8_e4m3fn)
+    v = torch.zeros(2, 256, 128, device="cuda").to(torch.float8_e4m3fn)
+    with pytest.raises(ValueError, match=r"head_dim must be in \[1, 128\]"):
         hb.fp8_attention(q, q, v, 1, 2)
+
+
+@pytest.mark.parametrize("d", [32, 80, 96, 17])
+def test_head_dims_between_the_kernel_sizes(hb, d):
+    """head_dim other than 64 / 128 (the reference pads to a power of two and masks): zero-padded columns,
+    the softmax scale of the real head_dim."""
+    g = torch.Generator().manual_seed(d)
+    bh, s = 4, 256
+    q8, k8, v8 = (torch.randn(bh, s, d, generator=g).to(torch.float8_e4m3fn) for _ in range(3))
+    blk8, blk_raw = o.fp8_attention(bits(q8), bits(k8), bits(v8.permute(0, 2, 1)), 2, 2, return_parts=True, block_n=128)
+    for v_dev in (v8.cuda().permute(0, 2, 1), v8.cuda().permute(0, 2, 1).contiguous()):
+        got = hb.fp8_attention(q8.cuda(), k8.cuda(), v_dev, 2, 2, out_dtype=torch.float32)
+        got8 = hb.fp8_attention(q8.cuda(), k8.cuda(), v_dev, 2, 2)
+        assert tuple(got.shape) == (2, 2, s, d) and got.is_contiguous() and got8.dtype == torch.float8_e4m3fn
+        assert_near_bit_exact(got.cpu().numpy(), bits(got8), blk_raw, blk8)
+    torch.cuda.synchronize()
+    _lib.check_status(0)
 
 
 @pytest.mark.parametrize("s,sk,d,causal", [(100, 100, 64, False), (72, 200, 128, False), (36, 77, 64, True), (129, 129, 128, True)])
