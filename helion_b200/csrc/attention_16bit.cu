@@ -108,6 +108,10 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const WaitCtx wctx{abort_flag, status};
 
   if (threadIdx.x == 0) {
+    // descriptor fetches overlap the barrier set-up and the tensor-memory allocation
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
     mbar_init(q_full, 1);
     mbar_init(q_empty, 2 + A16_SOFTMAX_THREADS);  // last Q K^T + every softmax thread and the P V thread hold the tile id
     mbar_init(s_full, 1);
@@ -143,9 +147,6 @@ attention16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     if (warp == w_producer) {
       // ------------------------------- TMA producer ------------------------------------------
       if (lane == 0) {
-        tma_prefetch_desc(&tmap_q);
-        tma_prefetch_desc(&tmap_k);
-        tma_prefetch_desc(&tmap_v);
         uint32_t slot_it = 0;
         uint32_t tile_iter = 0;
         bool ok = true;

@@ -135,6 +135,10 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const WaitCtx wctx{abort_flag, status};
 
   if (threadIdx.x == 0) {
+    // descriptor fetches overlap the barrier set-up and the tensor-memory allocation
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
     mbar_init(q_full, 1);
     // last Q K^T of the tile + every softmax thread and the P V thread have the tile id
     mbar_init(q_empty, 2 + ATT_SOFTMAX_THREADS);
@@ -174,9 +178,6 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     if (warp == w_producer) {
       // ------------------------------- TMA producer ------------------------------------------
       if (lane == 0) {
-        tma_prefetch_desc(&tmap_q);
-        tma_prefetch_desc(&tmap_k);
-        tma_prefetch_desc(&tmap_v);
         uint32_t slot_it = 0;  // running K/V tile counter (ring position)
         uint32_t tile_iter = 0;
         bool ok = true;

@@ -183,6 +183,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const WaitCtx wctx{abort_flag, status};
 
   if (threadIdx.x == 0) {
+    // descriptor fetches overlap the barrier set-up and the tensor-memory allocation
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -208,8 +211,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   if (warp == 0) {
     // ------------------------------- TMA producer --------------------------------------------
     if (lane == 0) {
-      tma_prefetch_desc(&tmap_a);
-      tma_prefetch_desc(&tmap_b);
       uint32_t it = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
@@ -443,6 +444,10 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const WaitCtx wctx{abort_flag, status};
 
   if (threadIdx.x == 0) {
+    // descriptor fetches overlap the barrier set-up and the tensor-memory allocation
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_out);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -469,8 +474,6 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs) --------------------------------
     if (lane == 0) {
-      tma_prefetch_desc(&tmap_a);
-      tma_prefetch_desc(&tmap_b);
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
@@ -666,6 +669,10 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const WaitCtx wctx{abort_flag, status};
 
   if (threadIdx.x == 0) {
+    // descriptor fetches overlap the barrier set-up and the tensor-memory allocation
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_out);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -691,8 +698,6 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs) --------------------------------
     if (lane == 0) {
-      tma_prefetch_desc(&tmap_a);
-      tma_prefetch_desc(&tmap_b);
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {

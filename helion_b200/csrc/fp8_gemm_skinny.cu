@@ -76,6 +76,9 @@ fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   const WaitCtx wctx{abort_flag, status};
 
   if (threadIdx.x == 0) {
+    // descriptor fetches overlap the barrier set-up and the tensor-memory allocation
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -101,8 +104,6 @@ fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   if (warp == 0) {
     // ------------------------------- TMA producer --------------------------------------------
     if (lane == 0) {
-      tma_prefetch_desc(&tmap_w);
-      tma_prefetch_desc(&tmap_x);
       uint32_t it = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
