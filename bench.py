@@ -566,6 +566,37 @@ def run_only(args, torch, dev, hb, _lib, emit) -> None:
           "tflops": flops / (med * 1e-3) / 1e12, "gbs": byts / (med * 1e-3) / 1e9})
 
 
+def decode_graph(hb, torch, dev, m: int, timed, peaks, layers: int = 32) -> dict:
+    """`layers` MLP GEMMs ([m, 4096] x [4096, 14336], one weight each) captured in one CUDA graph."""
+    g = torch.Generator(device=dev).manual_seed(2)
+    xa = torch.randn(m, MLP_K, device=dev, generator=g).to(torch.float8_e4m3fn)
+    ws = []
+    for _ in range(layers):
+        w = torch.randn(MLP_N, MLP_K, device=dev, generator=g) * 0.02
+        ws.append((w * (448.0 / w.abs().max())).to(torch.float8_e4m3fn).t())
+    outm = torch.empty(m, MLP_N, dtype=torch.bfloat16, device=dev)
+
+    def loop():
+        for w in ws:
+            hb.fp8_gemm(xa, w, out_dtype=torch.bfloat16, out=outm)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        loop()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        loop()
+    med, mn = timed(graph.replay, steps=10)
+    byts = m * MLP_K + MLP_K * MLP_N + 2 * m * MLP_N
+    gbs = layers * byts / (med * 1e-3) / 1e9
+    return {"layers": layers, "us_per_layer": med * 1e3 / layers, "us_per_layer_min": mn * 1e3 / layers,
+            "tflops": layers * 2.0 * m * MLP_N * MLP_K / (med * 1e-3) / 1e12, "hbm_gbs": gbs,
+            "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
+
+
 def run_extras(hb, _lib, o, torch, dev, flush, fp8_peak, peaks) -> dict:
     """Other benchmark configurations, measured in the same run (20 timed launches each)."""
     res = {}
@@ -605,6 +636,16 @@ def run_extras(hb, _lib, o, torch, dev, flush, fp8_peak, peaks) -> dict:
         e = entry(name)
         res["attention_preprocess_fp16"][name] = {"ms": e["ms"], "hbm_gbs": e["hbm_gbs"],
                                                   "frac_of_measured_hbm": e["frac_of_measured_hbm"]}
+
+    # The few-row MLP shapes as a decode loop sees them: 32 layers (32 different weights, 1.9 GB: nothing
+    # stays in L2) launched back to back from one CUDA graph, so neither launch latency nor the event
+    # pair around a single 20 us kernel is in the number.
+    res["mlp_decode_graph_32_layers"] = {}
+    for m in (16, 128):
+        try:
+            res["mlp_decode_graph_32_layers"][f"M{m}"] = decode_graph(hb, torch, dev, m, timed, peaks)
+        except Exception as ex:  # context only
+            res["mlp_decode_graph_32_layers"][f"M{m}"] = {"error": str(ex)[:120]}
 
     # cuBLASLt on the same workload, for context (the reference's GPU baseline, examples/fp8_gemm.py:61-78)
     try:
