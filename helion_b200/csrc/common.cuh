@@ -315,6 +315,16 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
   else umma_f16_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
 }
 
+// Programmatic dependent launch.  A kernel launched with launch_pdl() (host.h) may be scheduled while the
+// kernel before it in the stream is still running: everything up to pdl_wait() -- barrier set-up,
+// tensor-memory allocation, descriptor prefetch -- then overlaps that kernel's tail.  pdl_wait() returns
+// once the previous kernel has completed and its writes are visible, so no global memory is touched
+// before it.  pdl_launch_dependents() lets the NEXT kernel's CTAs be scheduled as soon as every CTA of
+// this grid has called it (they take an SM's resources as this grid's CTAs leave and park in their own
+// pdl_wait()).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Arrive on an mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

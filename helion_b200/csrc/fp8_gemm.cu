@@ -207,6 +207,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above overlapped the previous kernel's tail (launch_pdl); global memory from here on
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------- TMA producer --------------------------------------------
@@ -996,10 +999,9 @@ int launch_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, co
     }
   }
   const int grid = static_cast<int>(std::min<int64_t>(num_tiles * splits, ctx->num_sms));
-  kernel<<<grid, NUM_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, a.out, static_cast<int>(a.M), static_cast<int>(a.N),
-                                                         k_bytes<KIND>(a), a.ldc, group_m, ctx->status_dev, splits,
-                                                         static_cast<float*>(a.workspace), epi_scale(a));
-  HB_CUDA_CHECK(cudaGetLastError());
+  HB_CUDA_CHECK(launch_pdl(kernel, static_cast<unsigned>(grid), NUM_THREADS, L::SMEM_BYTES, a.stream, ta, tb, a.out,
+                           static_cast<int>(a.M), static_cast<int>(a.N), k_bytes<KIND>(a), a.ldc, group_m, ctx->status_dev,
+                           splits, static_cast<float*>(a.workspace), epi_scale(a)));
   return splits > 1 ? launch_splitk_reduce(a, splits) : HB200_OK;
 }
 

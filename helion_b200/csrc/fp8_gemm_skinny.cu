@@ -100,6 +100,9 @@ fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above overlapped the previous kernel's tail (launch_pdl); global memory from here on
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------- TMA producer --------------------------------------------
@@ -256,10 +259,9 @@ int launch_skinny_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap&
   }
   const int64_t n_tiles = (a.N + SK_BN - 1) / SK_BN;
   const int grid = static_cast<int>(std::min<int64_t>(n_tiles * splits, ctx->num_sms));
-  kernel<<<grid, SK_THREADS, L::SMEM_BYTES, a.stream>>>(tw, tx, a.out, static_cast<int>(a.M), static_cast<int>(a.N),
-                                                        static_cast<int>(a.K), a.ldc, ctx->status_dev, splits,
-                                                        static_cast<float*>(a.workspace), epi_scale(a));
-  HB_CUDA_CHECK(cudaGetLastError());
+  HB_CUDA_CHECK(launch_pdl(kernel, static_cast<unsigned>(grid), SK_THREADS, L::SMEM_BYTES, a.stream, tw, tx, a.out,
+                           static_cast<int>(a.M), static_cast<int>(a.N), static_cast<int>(a.K), a.ldc, ctx->status_dev, splits,
+                           static_cast<float*>(a.workspace), epi_scale(a)));
   return HB200_OK;
 }
 

@@ -138,4 +138,23 @@ int launch_attention_preprocess(const void* q, const void* k, const void* v, voi
 int attn_num_configs();
 int attn_describe_config(int cfg_id, char* buf, int buf_len);
 
+// Launch with programmatic stream serialization allowed: the kernel may start while its predecessor in
+// the stream drains, and must call pdl_wait() (common.cuh) before it touches global memory.  After a
+// predecessor that never triggers early (any ordinary kernel or copy) this is a plain in-order launch.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem_bytes, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 }  // namespace hb
