@@ -441,8 +441,8 @@ def attention(
     if out_dtype not in (q_in.dtype, torch.float32):
         raise TypeError(f"attention out_dtype must be {q_in.dtype} or float32, got {out_dtype}")
     dev = _require_cuda(q_in, k_in, v_in)
-    q, k, v = (t.reshape(-1, t.shape[-2], d) for t in (q_in, k_in, v_in))
-    bh = q.shape[0]
+    bh = math.prod(q_in.shape[:-2])  # explicit: reshape(-1, ...) is ambiguous for tensors without elements
+    q, k, v = (t.reshape(bh, t.shape[-2], d) for t in (q_in, k_in, v_in))
     if bh == 0 or m_dim == 0:
         return torch.empty(q_in.shape, dtype=out_dtype, device=q_in.device)
     if n_dim == 0:
