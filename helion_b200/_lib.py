@@ -80,6 +80,10 @@ SIGNATURES = {
         [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64x3, _i64x3, _i64x3, _i64x3, ctypes.c_float, ctypes.c_int,
          ctypes.c_int, _vp, ctypes.c_size_t, ctypes.c_int, _vp],
     ),
+    "hb200_debug_softmax_ceiling": (
+        ctypes.c_int,
+        [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, ctypes.c_int, _vp],
+    ),
     "hb200_debug_wait_selftest": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, _vp]),
     "hb200_num_configs": (ctypes.c_int, [ctypes.c_int]),
     "hb200_describe_config": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_int]),

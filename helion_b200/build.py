@@ -20,7 +20,7 @@ OUT_DIR = PKG_DIR / "_C"
 LIB_PATH = OUT_DIR / "libhelion_b200.so"
 INCLUDE_DIR = PKG_DIR.parent / "include"
 
-SOURCES = ["api.cu", "fp8_gemm.cu", "fp8_gemm_skinny.cu", "fp8_attention.cu", "attention_16bit.cu", "quantize.cu"]
+SOURCES = ["api.cu", "fp8_gemm.cu", "fp8_gemm_skinny.cu", "fp8_attention.cu", "fp8_attention_pair.cu", "softmax_ceiling.cu", "attention_16bit.cu", "quantize.cu"]
 
 NVCC_FLAGS = [
     "-gencode",

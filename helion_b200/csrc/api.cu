@@ -50,6 +50,10 @@ DeviceCtx* get_device_ctx(int device) {
     return nullptr;
   }
   DeviceGuard guard(device);
+  if (!guard.ok()) {
+    set_error(HB200_ERR_CUDA, "cannot make device " + std::to_string(device) + " current");
+    return nullptr;  // not cached: a later call may succeed
+  }
   c.initialised = true;
   cudaDeviceProp prop;
   e = cudaGetDeviceProperties(&prop, device);
@@ -89,6 +93,13 @@ DeviceCtx* get_device_ctx(int device) {
     g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
   }
   return &c;
+}
+
+uint32_t* peek_status_dev(int device) {
+  if (device < 0 || device >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_ctx_mutex);
+  const DeviceCtx& c = g_ctx[device];
+  return (c.initialised && c.init_error == 0) ? c.status_dev : nullptr;
 }
 
 int ensure_tmap_encoder() {
@@ -204,11 +215,29 @@ int hb200_debug_wait_selftest(int device, int limit_ms, void* stream) {
   if (limit_ms < 1 || limit_ms > 1000) return set_error(HB200_ERR_BAD_CONFIG, "wait self-test: limit must be 1..1000 ms");
   DeviceCtx* ctx = get_device_ctx(device);
   if (ctx == nullptr) return device_init_error(device);
-  DeviceGuard guard(device);
+  HB_DEVICE_GUARD(device);
   selftest::wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
       ctx->status_dev, static_cast<unsigned long long>(limit_ms) * 1000000ull, nullptr);
   HB_CUDA_CHECK(cudaGetLastError());
   return HB200_OK;
+}
+
+int hb200_debug_softmax_ceiling(int wgs, int ctas_per_sm, int poly_of8, int mode, int steps, void* cycles, int device,
+                                void* stream) {
+  if (wgs < 1 || wgs > 2 || ctas_per_sm < 1 || ctas_per_sm > 2 || (wgs == 2 && ctas_per_sm != 1)) {
+    return set_error(HB200_ERR_BAD_CONFIG, "softmax_ceiling: 1 or 2 warpgroups per CTA; 2 CTAs per SM only with 1 warpgroup");
+  }
+  if (mode < 0 || mode > 3 || steps < 1 || steps > (1 << 20)) {
+    return set_error(HB200_ERR_BAD_CONFIG, "softmax_ceiling: mode must be 0..3 and steps 1..2^20");
+  }
+  if (cycles == nullptr || (reinterpret_cast<uintptr_t>(cycles) & 7u)) {
+    return set_error(HB200_ERR_ALIGN, "softmax_ceiling: cycles must be an 8-byte aligned device pointer");
+  }
+  DeviceCtx* ctx = get_device_ctx(device);
+  if (ctx == nullptr) return ctx_error_code(device);
+  HB_DEVICE_GUARD(device);
+  return launch_softmax_ceiling(wgs, ctas_per_sm, poly_of8, mode, steps, static_cast<unsigned long long*>(cycles), ctx,
+                                static_cast<cudaStream_t>(stream));
 }
 
 int hb200_num_configs(int op) {
@@ -228,8 +257,20 @@ size_t hb200_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_d
   return gemm_workspace_bytes(M, N, K, out_dtype, cfg_id);
 }
 
+// SM count the table choice is made for: that of the current device when one can be asked without creating
+// anything, else 148 (B200).  The launch itself always uses the count of the device it runs on.
+static int query_num_sms() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) {
+    return sms;
+  }
+  cudaGetLastError();  // no device: not an error of this call
+  return 148;
+}
+
 int hb200_fp8_gemm_select_config(int64_t M, int64_t N, int64_t K, int y_is_colmajor, int out_dtype) {
-  return gemm_select_config(M, N, K, y_is_colmajor != 0, out_dtype, 148);
+  return gemm_select_config(M, N, K, y_is_colmajor != 0, out_dtype, query_num_sms());
 }
 
 // Validation and launch shared by hb200_fp8_gemm (scale_mode 0) and hb200_fp8_gemm_scaled.
@@ -301,7 +342,7 @@ static int fp8_gemm_impl(const void* x, const void* y, void* out, int64_t M, int
   a.scale_a = scale_a;
   a.scale_b = scale_b;
   a.scale_mode = scale_mode;
-  DeviceGuard guard(device);
+  HB_DEVICE_GUARD(device);
   return launch_fp8_gemm(a, ctx);
 }
 
@@ -386,7 +427,7 @@ int hb200_gemm_16bit(const void* x, const void* y, void* out, int64_t M, int64_t
   a.kind = in_dtype == HB200_DT_FP16 ? 1 : 2;
   a.bias = bias;
   a.relu = relu != 0 ? 1 : 0;
-  DeviceGuard guard(device);
+  HB_DEVICE_GUARD(device);
   return launch_gemm_16bit(a, ctx);
 }
 
@@ -434,6 +475,13 @@ int hb200_fp8_gemm_splitk_static(const void* x, const void* y, void* out, int64_
     return set_error(HB200_ERR_ALIGN, "fp8_gemm_splitk_static: x, y and out must be 16-byte aligned");
   }
   if (device < 0 || device >= kMaxDevices) return set_error(HB200_ERR_CUDA, "device index out of range");
+  {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device >= count) {
+      cudaGetLastError();
+      return set_error(HB200_ERR_CUDA, "fp8_gemm_splitk_static: no such CUDA device");
+    }
+  }
   GemmArgs a;
   a.x = x;
   a.y = y;
@@ -451,7 +499,7 @@ int hb200_fp8_gemm_splitk_static(const void* x, const void* y, void* out, int64_
   a.workspace_bytes = 0;
   a.device = device;
   a.stream = static_cast<cudaStream_t>(stream);
-  DeviceGuard guard(device);
+  HB_DEVICE_GUARD(device);
   return launch_fp8_gemm_static_scratch(a, splits);
 }
 
@@ -523,7 +571,7 @@ static int fp8_attention_impl(const void* q, const void* k, const void* v, void*
   a.device = device;
   a.stream = static_cast<cudaStream_t>(stream);
   a.sched = nullptr;
-  DeviceGuard guard(device);
+  HB_DEVICE_GUARD(device);
   if (workspace != nullptr) {
     if (workspace_bytes < HB200_ATTN_WORKSPACE_BYTES) {
       return set_error(HB200_ERR_WORKSPACE, "fp8_attention: workspace smaller than HB200_ATTN_WORKSPACE_BYTES");
@@ -606,7 +654,7 @@ int hb200_attention_16bit(const void* q, const void* k, const void* v, void* out
   a.stream = static_cast<cudaStream_t>(stream);
   a.sched = nullptr;
   a.kind = in_dtype == HB200_DT_FP16 ? 1 : 2;
-  DeviceGuard guard(device);
+  HB_DEVICE_GUARD(device);
   if (workspace != nullptr) {
     if (workspace_bytes < HB200_ATTN_WORKSPACE_BYTES || (reinterpret_cast<uintptr_t>(workspace) & 15u)) {
       return set_error(HB200_ERR_WORKSPACE, "attention_16bit: workspace must be 16-byte aligned and hold HB200_ATTN_WORKSPACE_BYTES");
@@ -634,7 +682,7 @@ int hb200_fp8_attention_preprocess(const void* q, const void* k, const void* v, 
   }
   DeviceCtx* ctx = get_device_ctx(device);
   if (ctx == nullptr) return ctx_error_code(device);
-  DeviceGuard guard(device);
+  HB_DEVICE_GUARD(device);
   return launch_attention_preprocess(q, k, v, q8, k8, v8, count, src_dtype, ctx, static_cast<cudaStream_t>(stream));
 }
 

@@ -479,11 +479,8 @@ template <int D, int KIND, int OUT_DT>
 int launch_attn16(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv) {
   using L = Attn16Layout<D>;
   auto kernel = attention16_kernel<D, KIND, OUT_DT>;
-  static bool attr_set[64] = {};
-  if (!attr_set[a.device]) {
-    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
-    attr_set[a.device] = true;
-  }
+  static std::atomic<uint64_t> smem_attr_done{0};
+  HB_CUDA_CHECK(set_max_dynamic_smem_once(smem_attr_done, reinterpret_cast<const void*>(kernel), L::SMEM_BYTES, a.device));
   const int64_t m_tiles = (a.S + A16_BM - 1) / A16_BM;
   const int64_t num_tiles = a.BH * m_tiles;
   if (num_tiles > INT32_MAX) return set_error(HB200_ERR_BAD_SHAPE, "attention_16bit: too many tiles");

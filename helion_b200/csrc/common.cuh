@@ -43,6 +43,8 @@ enum WaitSite : uint32_t {
   SITE_ATTN_P_FULL = 16,
   SITE_ATTN_PV_DONE = 17,
   SITE_ATTN_O_FULL = 18,
+  SITE_ATTN_ALPHA = 19,
+  SITE_ATTN_O_READY = 20,
   SITE_SELFTEST = 40,
 };
 
@@ -367,6 +369,12 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -614,6 +622,36 @@ __device__ __forceinline__ uint64_t exp2_pair_poly(uint64_t x2) {
   uint64_t p = ffma2(pack2f(0.055171605f, 0.055171605f), f, pack2f(0.24261111f, 0.24261111f));
   p = ffma2(p, f, pack2f(0.69326097f, 0.69326097f));
   p = ffma2(p, f, pack2f(0.99992806f, 0.99992806f));
+  uint32_t pl, ph, rl, rh;
+  unpack2(p, pl, ph);
+  unpack2(xr, rl, rh);
+  pl += rl << 23;  // exponent += round(x); the bits above the exponent wrap away
+  ph += rh << 23;
+  return pack2(pl, ph);
+}
+
+// Same split as exp2_pair_poly with a degree-5 polynomial (relative error 2.4e-7, the size of
+// ex2.approx's own error): a value computed this way rounds to the same e4m3 code as the MUFU result
+// except where either lies within that distance of a rounding boundary, so rows of the attention table
+// that follow the reference's running max bit for bit may use it for part of their exponentials.
+__device__ __forceinline__ uint64_t exp2_pair_poly5(uint64_t x2) {
+  uint32_t xl, xh;
+  unpack2(x2, xl, xh);
+  const float xcl = fmaxf(__uint_as_float(xl), -126.0f);
+  const float xch = fmaxf(__uint_as_float(xh), -126.0f);
+  const uint64_t x = pack2f(xcl, xch);
+  const uint64_t magic = pack2f(12582912.0f, 12582912.0f);
+  const uint64_t neg_magic = pack2f(-12582912.0f, -12582912.0f);
+  const uint64_t neg_one = pack2f(-1.0f, -1.0f);
+  const uint64_t xr = fadd2(x, magic);       // low mantissa bits now hold round(x)
+  const uint64_t nf = fadd2(xr, neg_magic);  // round(x) as a float
+  const uint64_t f = ffma2(nf, neg_one, x);  // x - round(x), in [-0.5, 0.5]
+  uint64_t p = ffma2(pack2f(0.001327647129073739f, 0.001327647129073739f), f,
+                     pack2f(0.009675540961325169f, 0.009675540961325169f));
+  p = ffma2(p, f, pack2f(0.05550713092088699f, 0.05550713092088699f));
+  p = ffma2(p, f, pack2f(0.24022120237350464f, 0.24022120237350464f));
+  p = ffma2(p, f, pack2f(0.6931469440460205f, 0.6931469440460205f));
+  p = ffma2(p, f, pack2f(1.0000001192092896f, 1.0000001192092896f));
   uint32_t pl, ph, rl, rh;
   unpack2(p, pl, ph);
   unpack2(xr, rl, rh);

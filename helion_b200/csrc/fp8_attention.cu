@@ -553,21 +553,31 @@ fp8_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 }
 
 struct AttnConfig {
-  int poly_of8;  // of every 8 pairs of exponentials, how many use the FMA-pipe polynomial
+  int poly_of8;  // of every 8 pairs of exponentials, how many use an FMA-pipe polynomial
   bool lazy;     // rescale O only when a row max grew by more than 2^8
   int bn;        // keys per step; 64 exists for head_dim 64 only (head_dim 128 then runs 128-key steps)
+  bool pair;     // two query tiles per CTA (fp8_attention_pair.cu); problems it does not take run the row's one-tile form
   const char* note;
 };
 const AttnConfig kAttnConfigs[] = {
-    {0, false, 128, "exact running max (rescale whenever a row max moves), all exp2 on the MUFU unit"},
-    {0, true, 128, "lazy rescale (only when a row max grew by more than 2^8), all exp2 on the MUFU unit"},
-    {2, true, 128, "lazy rescale, 2 of 8 exp2 pairs on the FMA pipes (degree-3 polynomial)"},
-    {4, true, 128, "lazy rescale, 4 of 8 exp2 pairs on the FMA pipes"},
-    {0, false, 64, "exact running max, 64-key steps with four CTAs per SM for head_dim 64 (128-key steps otherwise)"},
-    {0, true, 64, "lazy rescale, 64-key steps with four CTAs per SM for head_dim 64 (128-key steps otherwise)"},
+    {0, false, 128, false, "exact running max (rescale whenever a row max moves), all exp2 on the MUFU unit"},
+    {0, true, 128, false, "lazy rescale (only when a row max grew by more than 2^8), all exp2 on the MUFU unit"},
+    {2, true, 128, false, "lazy rescale, 2 of 8 exp2 pairs on the FMA pipes (degree-3 polynomial)"},
+    {4, true, 128, false, "lazy rescale, 4 of 8 exp2 pairs on the FMA pipes"},
+    {0, false, 64, false, "exact running max, 64-key steps with four CTAs per SM for head_dim 64 (128-key steps otherwise)"},
+    {0, true, 64, false, "lazy rescale, 64-key steps with four CTAs per SM for head_dim 64 (128-key steps otherwise)"},
+    {0, false, 128, true, "two query tiles per CTA, exact running max, all exp2 on the MUFU unit"},
+    {2, false, 128, true, "two query tiles per CTA, exact running max, 2 of 8 exp2 pairs on the FMA pipes (degree-5 polynomial)"},
+    {3, false, 128, true, "two query tiles per CTA, exact running max, 3 of 8 exp2 pairs on the FMA pipes (degree-5 polynomial)"},
+    {4, false, 128, true, "two query tiles per CTA, exact running max, 4 of 8 exp2 pairs on the FMA pipes (degree-5 polynomial)"},
+    {4, true, 128, true, "two query tiles per CTA, lazy rescale, 4 of 8 exp2 pairs on the FMA pipes (degree-5 polynomial)"},
 };
-constexpr int kNumAttnConfigs = 6;
+constexpr int kNumAttnConfigs = 11;
 constexpr int kDefaultAttnConfig = 0;
+
+// The two-tile kernel takes unmasked problems with at least two row blocks per slice and at least two key
+// steps; everything else runs the one-tile kernel.
+bool attn_pair_applies(const AttnArgs& a) { return !a.causal && a.S > ATT_BM && a.Sk > 128; }
 
 // The row used for cfg_id = -1: always an exact-running-max row.  Measured on B200 (B8 H32, cold L2):
 // head_dim 64 at 4096 keys runs 1540 us with 64-key steps and four CTAs per SM against 1665 us with
@@ -585,11 +595,8 @@ int launch_attn_poly(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, c
                      const CUtensorMap& tv) {
   using L = AttnLayout<D, BN>;
   auto kernel = fp8_attention_kernel<D, BN, V_KMAJOR, OUT_DT, POLY_OF8, LAZY>;
-  static bool attr_set[64] = {};
-  if (!attr_set[a.device]) {
-    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
-    attr_set[a.device] = true;
-  }
+  static std::atomic<uint64_t> smem_attr_done{0};
+  HB_CUDA_CHECK(set_max_dynamic_smem_once(smem_attr_done, reinterpret_cast<const void*>(kernel), L::SMEM_BYTES, a.device));
   const int64_t m_tiles = (a.S + ATT_BM - 1) / ATT_BM;
   const int64_t num_tiles = a.BH * m_tiles;
   if (num_tiles > INT32_MAX) return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: too many tiles");
@@ -685,6 +692,12 @@ int launch_fp8_attention(const AttnArgs& args, DeviceCtx* ctx) {
                           bn == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
       if (rc != HB200_OK) return rc;
     }
+  }
+  if (kAttnConfigs[a.cfg_id].pair) {
+    if (attn_pair_applies(a)) {
+      return launch_fp8_attention_pair(a, ctx, tq, tk, tv, v_kmajor, kAttnConfigs[a.cfg_id].poly_of8, kAttnConfigs[a.cfg_id].lazy);
+    }
+    a.cfg_id = kAttnConfigs[a.cfg_id].lazy ? 1 : 0;  // the row's one-tile form (same tensor maps: 128-key steps)
   }
   if (a.D == 64) {
     return v_kmajor ? launch_attn_by_dtype<64, true>(a, ctx, tq, tk, tv)

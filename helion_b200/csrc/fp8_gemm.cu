@@ -473,6 +473,9 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above may overlap the previous kernel's tail (launch_pdl); global memory from here on
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs) --------------------------------
@@ -697,6 +700,9 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above may overlap the previous kernel's tail (launch_pdl); global memory from here on
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs) --------------------------------
@@ -896,11 +902,8 @@ template <int STAGES, bool B_MN, int OUT_DT, int KIND = KIND_E4M3>
 int launch_pair_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
   using L = PairLayout<STAGES>;
   auto kernel = fp8_gemm_pair_kernel<STAGES, B_MN, OUT_DT, KIND>;
-  static bool attr_set[64] = {};
-  if (!attr_set[a.device]) {
-    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
-    attr_set[a.device] = true;
-  }
+  static std::atomic<uint64_t> smem_attr_done{0};
+  HB_CUDA_CHECK(set_max_dynamic_smem_once(smem_attr_done, reinterpret_cast<const void*>(kernel), L::SMEM_BYTES, a.device));
   const int64_t m_tiles = (a.M + PAIR_BM - 1) / PAIR_BM;
   const int64_t n_tiles = (a.N + PAIR_BN - 1) / PAIR_BN;
   const int64_t num_tiles = m_tiles * n_tiles;
@@ -910,10 +913,9 @@ int launch_pair_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& t
     int rc = encode_out_map<OUT_DT>(&tout, a);
     if (rc != HB200_OK) return rc;
   }
-  kernel<<<2 * pairs, NUM_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, tout, static_cast<int>(a.M),
-                                                              static_cast<int>(a.N), k_bytes<KIND>(a), group_m,
-                                                              ctx->status_dev, epi_scale(a));
-  HB_CUDA_CHECK(cudaGetLastError());
+  HB_CUDA_CHECK(launch_pdl(kernel, static_cast<unsigned>(2 * pairs), NUM_THREADS, L::SMEM_BYTES, a.stream, ta, tb, tout,
+                           static_cast<int>(a.M), static_cast<int>(a.N), k_bytes<KIND>(a), group_m, ctx->status_dev,
+                           epi_scale(a)));
   return HB200_OK;
 }
 
@@ -921,11 +923,8 @@ template <bool B_MN, int OUT_DT, int KIND = KIND_E4M3>
 int launch_pair2_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
   using L = Pair2Layout<4>;
   auto kernel = fp8_gemm_pair2_kernel<4, B_MN, OUT_DT, KIND>;
-  static bool attr_set[64] = {};
-  if (!attr_set[a.device]) {
-    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
-    attr_set[a.device] = true;
-  }
+  static std::atomic<uint64_t> smem_attr_done{0};
+  HB_CUDA_CHECK(set_max_dynamic_smem_once(smem_attr_done, reinterpret_cast<const void*>(kernel), L::SMEM_BYTES, a.device));
   const int64_t m_tiles = (a.M + PAIR2_BM - 1) / PAIR2_BM;
   const int64_t n_tiles = (a.N + PAIR2_BN - 1) / PAIR2_BN;
   const int pairs = static_cast<int>(std::min<int64_t>(m_tiles * n_tiles, ctx->num_sms / 2));
@@ -934,10 +933,9 @@ int launch_pair2_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& 
     int rc = encode_out_map<OUT_DT>(&tout, a);
     if (rc != HB200_OK) return rc;
   }
-  kernel<<<2 * pairs, PAIR2_THREADS, L::SMEM_BYTES, a.stream>>>(ta, tb, tout, static_cast<int>(a.M),
-                                                                static_cast<int>(a.N), k_bytes<KIND>(a), group_m,
-                                                                ctx->status_dev, epi_scale(a));
-  HB_CUDA_CHECK(cudaGetLastError());
+  HB_CUDA_CHECK(launch_pdl(kernel, static_cast<unsigned>(2 * pairs), PAIR2_THREADS, L::SMEM_BYTES, a.stream, ta, tb, tout,
+                           static_cast<int>(a.M), static_cast<int>(a.N), k_bytes<KIND>(a), group_m, ctx->status_dev,
+                           epi_scale(a)));
   return HB200_OK;
 }
 
@@ -982,11 +980,8 @@ int launch_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, co
                     int splits_requested = 1) {
   using L = GemmLayout<BN, STAGES>;
   auto kernel = fp8_gemm_kernel<BN, STAGES, B_MN, OUT_DT, KIND>;
-  static bool attr_set[64] = {};
-  if (!attr_set[a.device]) {
-    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
-    attr_set[a.device] = true;
-  }
+  static std::atomic<uint64_t> smem_attr_done{0};
+  HB_CUDA_CHECK(set_max_dynamic_smem_once(smem_attr_done, reinterpret_cast<const void*>(kernel), L::SMEM_BYTES, a.device));
   const int m_tiles = static_cast<int>((a.M + BM - 1) / BM);
   const int n_tiles = static_cast<int>((a.N + BN - 1) / BN);
   const int64_t num_tiles = static_cast<int64_t>(m_tiles) * n_tiles;
@@ -1166,10 +1161,12 @@ int launch_fp8_gemm_static_scratch(const GemmArgs& a_in, int splits_requested) {
   if (splits < 2) {
     return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm_splitk_static: K is too short to split (needs at least 2 blocks of 128)");
   }
-  const size_t need = static_cast<size_t>(splits) * a_in.M * a_in.N * sizeof(float);
-  if (need > HB200_STATIC_SCRATCH_BYTES) {
+  // M*N against the elements one split may take, by division: the product of the sizes cannot wrap that way
+  const uint64_t elems_per_split = HB200_STATIC_SCRATCH_BYTES / (sizeof(float) * static_cast<uint64_t>(splits));
+  if (static_cast<uint64_t>(a_in.M) > elems_per_split / static_cast<uint64_t>(a_in.N)) {
     return set_error(HB200_ERR_WORKSPACE,
-                     "fp8_gemm_splitk_static: splits*M*N*4 = " + std::to_string(need) + " bytes exceeds the static scratch of " +
+                     "fp8_gemm_splitk_static: splits*M*N*4 bytes (M = " + std::to_string(a_in.M) + ", N = " +
+                         std::to_string(a_in.N) + ", " + std::to_string(splits) + " splits) exceeds the static scratch of " +
                          std::to_string(HB200_STATIC_SCRATCH_BYTES) + " bytes; use hb200_fp8_gemm with a workspace");
   }
   StaticScratchState* st = &g_static_state[a_in.device];
@@ -1177,7 +1174,12 @@ int launch_fp8_gemm_static_scratch(const GemmArgs& a_in, int splits_requested) {
     // First call on this device (the device is current here): resolve the array's device address.
     std::lock_guard<std::mutex> lock(g_static_mutex);
     if (!st->ready) {
-      int major = 0, sms = 0;
+      int major = 0, sms = 0, current = -1;
+      // the symbol's address belongs to the CURRENT device: it must be the one this call is for
+      HB_CUDA_CHECK(cudaGetDevice(&current));
+      if (current != a_in.device) {
+        return set_error(HB200_ERR_CUDA, "fp8_gemm_splitk_static: device " + std::to_string(a_in.device) + " is not current");
+      }
       HB_CUDA_CHECK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, a_in.device));
       HB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, a_in.device));
       if (major != 10) return set_error(HB200_ERR_UNSUPPORTED_ARCH, "this library holds sm_100a code only");
@@ -1193,10 +1195,13 @@ int launch_fp8_gemm_static_scratch(const GemmArgs& a_in, int splits_requested) {
   GemmArgs a = a_in;
   a.workspace = st->scratch;
   a.workspace_bytes = HB200_STATIC_SCRATCH_BYTES;
-  DeviceCtx ctx;  // only the fields the launcher reads; no status word (a wait that runs out still aborts the kernel)
+  // Only the fields the launcher reads.  The status word belongs to the device context, which this entry
+  // point must not create (that allocates): it is used when another entry point has created it already;
+  // until then a wait that runs out here still ends the kernel early but is not reported.
+  DeviceCtx ctx;
   ctx.initialised = true;
   ctx.num_sms = st->num_sms;
-  ctx.status_dev = nullptr;
+  ctx.status_dev = peek_status_dev(a_in.device);
 
   CUtensorMap ta, tb;
   {

@@ -252,11 +252,8 @@ template <int NM, int OUT_DT>
 int launch_skinny_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, int splits) {
   using L = SkinnyLayout<NM>;
   auto kernel = fp8_gemm_skinny_kernel<NM, OUT_DT>;
-  static bool attr_set[64] = {};
-  if (!attr_set[a.device]) {
-    HB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES));
-    attr_set[a.device] = true;
-  }
+  static std::atomic<uint64_t> smem_attr_done{0};
+  HB_CUDA_CHECK(set_max_dynamic_smem_once(smem_attr_done, reinterpret_cast<const void*>(kernel), L::SMEM_BYTES, a.device));
   const int64_t n_tiles = (a.N + SK_BN - 1) / SK_BN;
   const int grid = static_cast<int>(std::min<int64_t>(n_tiles * splits, ctx->num_sms));
   HB_CUDA_CHECK(launch_pdl(kernel, static_cast<unsigned>(grid), SK_THREADS, L::SMEM_BYTES, a.stream, tw, tx, a.out,

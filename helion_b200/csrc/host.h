@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <string>
 
 #include "../../include/helion_b200.h"
@@ -39,19 +40,44 @@ const char* last_error_text();
     }                                                                                               \
   } while (0)
 
-// Switches the current device for the duration of a launch and restores it afterwards.
+// Raises a kernel's dynamic shared-memory limit once per device.  `done` is a bit mask of devices (one static
+// per kernel instance at the call site); concurrent first calls may both set the attribute, which is harmless.
+inline cudaError_t set_max_dynamic_smem_once(std::atomic<uint64_t>& done, const void* kernel, int bytes, int device) {
+  const uint64_t bit = 1ull << (static_cast<unsigned>(device) & 63u);
+  if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done.fetch_or(bit, std::memory_order_release);
+  return e;
+}
+
+// Switches the current device for the duration of a launch and restores it afterwards.  ok() is false when
+// the device could not be made current; the caller must then return an error instead of launching on
+// whatever device happens to be current.
 struct DeviceGuard {
   int prev = -1;
   bool switched = false;
+  bool good = false;
   explicit DeviceGuard(int device) {
-    if (cudaGetDevice(&prev) == cudaSuccess && prev != device) {
-      switched = cudaSetDevice(device) == cudaSuccess;
+    if (cudaGetDevice(&prev) != cudaSuccess) return;
+    if (prev == device) {
+      good = true;
+      return;
     }
+    switched = cudaSetDevice(device) == cudaSuccess;
+    good = switched;
   }
+  bool ok() const { return good; }
   ~DeviceGuard() {
     if (switched) cudaSetDevice(prev);
   }
 };
+#define HB_DEVICE_GUARD(device)   \
+  ::hb::DeviceGuard guard(device); \
+  if (!guard.ok()) return ::hb::set_error(HB200_ERR_CUDA, "cannot make device " + std::to_string(device) + " current")
+
+// The device-side alias of a device's status word if its context already exists, else nullptr.  Never creates
+// the context (so it allocates nothing); used by the entry point that must not allocate.
+uint32_t* peek_status_dev(int device);
 
 // Encode a tiled tensor map over bytes.  dims/strides innermost first; strides[i] is the byte
 // stride of dimension i+1 (dimension 0 is contiguous).  Returns HB200_OK or an error code.
@@ -135,6 +161,12 @@ int launch_attention_16bit(const AttnArgs& args, DeviceCtx* ctx);
 // q, k, v (fp16 / bf16 / fp32, `count` elements each) -> e4m3fn with torch's cast rule (quantize.cu).
 int launch_attention_preprocess(const void* q, const void* k, const void* v, void* q8, void* k8, void* v8, int64_t count,
                                 int src_dtype, DeviceCtx* ctx, cudaStream_t stream);
+// The two-tile attention kernel (fp8_attention_pair.cu) on tensor maps built for 128-key steps; non-causal only.
+int launch_fp8_attention_pair(const AttnArgs& args, DeviceCtx* ctx, const CUtensorMap& tq, const CUtensorMap& tk,
+                              const CUtensorMap& tv, bool v_kmajor, int poly_of8, bool lazy);
+// Softmax-only ceiling kernel (softmax_ceiling.cu): `cycles` receives one SM-clock count per CTA.
+int launch_softmax_ceiling(int wgs, int ctas_per_sm, int poly_of8, int mode, int steps, unsigned long long* cycles,
+                           DeviceCtx* ctx, cudaStream_t stream);
 int attn_num_configs();
 int attn_describe_config(int cfg_id, char* buf, int buf_len);
 

@@ -10,7 +10,9 @@ back); done one after the other on one stream they take ~15x longer than the 819
   block i-1 is already on its way back (row blocks of a GEMM are independent, the same fact the
   multi-GPU sharding uses);
 * the device buffers exist ``depth`` times, so the next call's uploads overlap this call's
-  downloads.
+  downloads;
+* ``y`` may be made resident (:meth:`HostGemm.set_weight`): a weight that is the same for every call is
+  uploaded once, and a call then moves only ``x`` up and ``out`` back.
 
 The arithmetic is that of :func:`helion_b200.ops.fp8_gemm` on every row block, so the result is
 bit-identical to one call on the whole matrix.
@@ -46,19 +48,44 @@ class HostGemm:
         self.depth = depth
         self._slot = 0
         self._in, self._compute, self._out = (torch.cuda.Stream(self.device) for _ in range(3))
-        self._x = [torch.empty(m, k, dtype=torch.uint8, device=self.device) for _ in range(depth)]
-        self._y = [torch.empty(n, k, dtype=torch.uint8, device=self.device) for _ in range(depth)]
-        self._o = [torch.empty(m, n, dtype=out_dtype, device=self.device) for _ in range(depth)]
+        # The buffers are only ever used on the three private streams; they are allocated under one of them and
+        # recorded on the others, so that torch's caching allocator does not hand them to other work while
+        # copies or kernels of a dropped pipeline are still in flight.
+        with torch.cuda.stream(self._compute):
+            self._x = [torch.empty(m, k, dtype=torch.uint8, device=self.device) for _ in range(depth)]
+            self._y = [torch.empty(n, k, dtype=torch.uint8, device=self.device) for _ in range(depth)]
+            self._o = [torch.empty(m, n, dtype=out_dtype, device=self.device) for _ in range(depth)]
+            self._w = torch.empty(n, k, dtype=torch.uint8, device=self.device)
+        for t in (*self._x, *self._y, *self._o, self._w):
+            t.record_stream(self._in)
+            t.record_stream(self._out)
+        self._w_ready: Optional[torch.cuda.Event] = None
         self._done: List[Optional[torch.cuda.Event]] = [None] * depth
 
-    def submit(self, x_host: torch.Tensor, y_host: torch.Tensor, out_host: torch.Tensor) -> torch.cuda.Event:
-        """Enqueue one GEMM; returns the event that fires when ``out_host`` is complete."""
+    def set_weight(self, y_host: torch.Tensor) -> None:
+        """Upload ``y`` (stored as ``[N, K]`` bytes, i.e. column-major) once; later calls of :meth:`submit` with
+        ``y_host=None`` multiply by it without moving it again."""
+        if tuple(y_host.shape) != (self.n, self.k):
+            raise ValueError(f"expected y stored as [{self.n},{self.k}]")
+        self.synchronize()  # no call in flight may still read the previous weight
+        self._in.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self._in):
+            self._w.copy_(y_host.view(torch.uint8), non_blocking=True)
+            self._w_ready = torch.cuda.Event()
+            self._w_ready.record(self._in)
+
+    def submit(self, x_host: torch.Tensor, y_host: Optional[torch.Tensor], out_host: torch.Tensor) -> torch.cuda.Event:
+        """Enqueue one GEMM; returns the event that fires when ``out_host`` is complete.  ``y_host=None`` uses
+        the resident weight of :meth:`set_weight`."""
         m, n, k = self.m, self.n, self.k
-        if tuple(x_host.shape) != (m, k) or tuple(y_host.shape) != (n, k) or tuple(out_host.shape) != (m, n):
+        if tuple(x_host.shape) != (m, k) or tuple(out_host.shape) != (m, n) or (
+                y_host is not None and tuple(y_host.shape) != (n, k)):
             raise ValueError(f"expected x [{m},{k}], y stored as [{n},{k}], out [{m},{n}]")
+        if y_host is None and self._w_ready is None:
+            raise ValueError("no resident weight: call set_weight(y_host) first or pass y_host")
         if out_host.dtype != self.out_dtype:
             raise TypeError(f"out_host must be {self.out_dtype}")
-        xh, yh = x_host.view(torch.uint8), y_host.view(torch.uint8)
+        xh = x_host.view(torch.uint8)
         slot = self._slot
         self._slot = (slot + 1) % self.depth
         xd, yd, od = self._x[slot], self._y[slot], self._o[slot]
@@ -69,7 +96,11 @@ class HostGemm:
         blocks = [(r, min(r + self.block_rows, m)) for r in range(0, m, self.block_rows)]
         arrived = []
         with torch.cuda.stream(self._in):
-            yd.copy_(yh, non_blocking=True)
+            if y_host is not None:
+                yd.copy_(y_host.view(torch.uint8), non_blocking=True)
+            else:
+                yd = self._w
+                self._in.wait_event(self._w_ready)
             for r0, r1 in blocks:
                 xd[r0:r1].copy_(xh[r0:r1], non_blocking=True)
                 ev = torch.cuda.Event()
@@ -102,3 +133,15 @@ class HostGemm:
         for ev in self._done:
             if ev is not None:
                 ev.synchronize()
+
+    def close(self) -> None:
+        """Wait for everything in flight; call before dropping a pipeline whose last results were not awaited."""
+        self.synchronize()
+        for stream in (self._in, self._compute, self._out):
+            stream.synchronize()
+
+    def __del__(self) -> None:
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown: CUDA may be gone already
+            pass

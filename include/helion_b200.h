@@ -205,13 +205,20 @@ HB200_API int hb200_fp8_attention_preprocess(const void* q, const void* k, const
  *     HB200_ERR_WORKSPACE when that exceeds the array (use hb200_fp8_gemm with a workspace then);
  *   - splits: 2..8 (the K range is cut into that many parts; every part of every output element is
  *     written before it is read, so the array needs no clearing between calls);
- *   - the first call on a device looks up the array's device address (no allocation); make that
- *     first call before starting any stream capture;
+ *   - the first call on a device looks up the array's device address, and the first call for each
+ *     (out_dtype, layout of y) on a device raises that kernel instance's shared-memory limit and lets
+ *     the driver load it (no allocation by this library); make one warm-up call per (out_dtype, layout)
+ *     you will use before starting any stream capture or entering a section that must not allocate;
+ *   - a device-side wait that runs out (hb200_read_status) is reported for this entry point only once
+ *     the device's context exists, i.e. after any other entry point of this library has run on the
+ *     device; before that such a wait still ends the kernel early, but nothing records it, because
+ *     creating the context allocates;
  *   - all calls on a device share the one array: two calls whose kernels can overlap on the GPU
  *     (different streams, no dependency between them) race on it and give wrong results -- order them;
  *   - calls neither cudaMalloc nor cudaFree nor any allocating library routine; launches two kernels
  *     (partial products, then the ordered sum and conversion) on the given stream.
- * x, y, out, sizes, strides, out_dtype and the return codes are those of hb200_fp8_gemm. */
+ * x, y, out, sizes, strides, out_dtype and the return codes are those of hb200_fp8_gemm (plus
+ * HB200_ERR_CUDA when `device` does not exist or cannot be made current). */
 #define HB200_STATIC_SCRATCH_BYTES (4u << 20)
 HB200_API int hb200_fp8_gemm_splitk_static(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t K,
                                            int64_t x_rs, int64_t x_cs, int64_t y_rs, int64_t y_cs, int64_t out_rs,
@@ -235,6 +242,18 @@ HB200_API int hb200_reset_status(int device);
  * reference: Helion's only timeout handling is around Triton compilation,
  * helion/autotuner/base_search.py:155-200.) */
 HB200_API int hb200_debug_wait_selftest(int device, int limit_ms, void* stream);
+
+/* Softmax-only ceiling of the attention kernels: runs nothing but the per-score work of
+ * examples/fp8_attention.py:74-94 (row max, exp2, row sum, cast of P to e4m3, with the scores read from and
+ * P written to tensor memory) for `steps` 128x128 steps per softmax warpgroup, on every SM.
+ *   wgs: softmax warpgroups per CTA (1 or 2); ctas_per_sm: 1 or 2 (2 only with wgs = 1);
+ *   poly_of8: of every 8 pairs of exponentials, how many run as a polynomial on the FMA pipes (0, 2, 3, 4);
+ *   mode: 0 full step, 1 without the row max, 2 without the exponentials, 3 tensor-memory traffic only;
+ *   cycles: device pointer to num_sms * ctas_per_sm uint64: SM clocks the slowest warp of each CTA took.
+ * Cycles per step per SM = cycles / (steps * wgs * ctas_per_sm): the floor for any pipeline built around this
+ * arithmetic.  A measurement aid; the reference has no counterpart. */
+HB200_API int hb200_debug_softmax_ceiling(int wgs, int ctas_per_sm, int poly_of8, int mode, int steps, void* cycles,
+                                          int device, void* stream);
 
 /* Number of SMs the persistent kernels size their grids with (cudaDevAttrMultiProcessorCount;
  * the role of helion/runtime/__init__.py:41-52 `get_num_sm`). */

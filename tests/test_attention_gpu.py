@@ -80,15 +80,15 @@ def assert_near_bit_exact(got32, got8, blk_raw, blk8):
         assert (got8 == o.e4m3_encode(blk8)).mean() >= 0.995
 
 
-def compare(hb, batch, heads, seq, dim, seed, v_contiguous):
+def compare(hb, batch, heads, seq, dim, seed, v_contiguous, config=None):
     (q8, k8, v8), (qd, kd, vd) = make_inputs(batch, heads, seq, dim, seed, v_contiguous)
     qb, kb, vb = bits(q8), bits(k8), bits(v8)
     one8, one_raw = o.fp8_attention(qb, kb, vb, batch, heads, return_parts=True)
     blk8, blk_raw = o.fp8_attention(qb, kb, vb, batch, heads, return_parts=True, block_n=128)
 
-    out8 = hb.fp8_attention(qd, kd, vd, batch, heads)
-    out32 = hb.fp8_attention(qd, kd, vd, batch, heads, out_dtype=torch.float32)
-    outbf = hb.fp8_attention(qd, kd, vd, batch, heads, out_dtype=torch.bfloat16)
+    out8 = hb.fp8_attention(qd, kd, vd, batch, heads, config=config)
+    out32 = hb.fp8_attention(qd, kd, vd, batch, heads, out_dtype=torch.float32, config=config)
+    outbf = hb.fp8_attention(qd, kd, vd, batch, heads, out_dtype=torch.bfloat16, config=config)
     assert out8.dtype == torch.float8_e4m3fn and tuple(out8.shape) == (batch, heads, seq, dim)
     got8, got32, gotbf = bits(out8), out32.cpu().numpy(), outbf.float().cpu().numpy()
     assert np.isfinite(got32).all()
@@ -116,6 +116,70 @@ def compare(hb, batch, heads, seq, dim, seed, v_contiguous):
 )
 def test_matches_oracle(hb, batch, heads, seq, dim, v_contiguous):
     compare(hb, batch, heads, seq, dim, seed=100 + seq + dim, v_contiguous=v_contiguous)
+
+
+PAIR_EXACT_ROWS = [6, 7, 8, 9]  # two query tiles per CTA, exact running max, 0 / 2 / 3 / 4 of 8 exp2 pairs as a polynomial
+
+
+@pytest.mark.parametrize("config", PAIR_EXACT_ROWS)
+@pytest.mark.parametrize("v_contiguous", [False, True], ids=["v_physical_SD", "v_contiguous_DS"])
+@pytest.mark.parametrize(
+    "batch,heads,seq,dim",
+    [(2, 4, 256, 64), (1, 2, 512, 128), (2, 3, 1024, 64), (1, 2, 1040, 128), (1, 3, 208, 128), (1, 1, 384, 64),
+     (5, 7, 144, 64), (1, 40, 384, 128), (1, 2, 2048, 128)],
+)
+def test_two_tile_rows_match_oracle(hb, batch, heads, seq, dim, v_contiguous, config):
+    """Rows 6-9 (two query tiles per CTA) follow the reference's loop at 128-key blocks like row 0, with part of
+    the exponentials as a degree-5 polynomial whose error is that of ex2.approx: the same two gates as the
+    default row.  Shapes with an odd number of row blocks (the second tile of the last pair runs on zero fill),
+    ragged rows and keys, and more units than SMs."""
+    compare(hb, batch, heads, seq, dim, seed=300 + seq + dim, v_contiguous=v_contiguous, config=config)
+    torch.cuda.synchronize()
+    _lib.check_status(0)
+
+
+@pytest.mark.parametrize("batch,heads,seq,dim", [(2, 4, 256, 64), (1, 2, 1040, 128), (3, 50, 384, 64), (1, 40, 2048, 128)])
+def test_two_tile_row_without_polynomial_equals_row_0(hb, batch, heads, seq, dim):
+    """Row 6 runs the arithmetic of row 0 (same per-row instruction stream, same order of the tensor-core sums,
+    the same rescale products) in a different pipeline: every output bit must agree.  Both tile orders."""
+    _, (qd, kd, vd) = make_inputs(batch, heads, seq, dim, seed=23, v_contiguous=False)
+    for dt in (torch.float32, torch.float8_e4m3fn, torch.bfloat16):
+        want = hb.fp8_attention(qd, kd, vd, batch, heads, out_dtype=dt, config=0, balanced=False)
+        for balanced in (False, True):
+            got = hb.fp8_attention(qd, kd, vd, batch, heads, out_dtype=dt, config=6, balanced=balanced)
+            assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
+    torch.cuda.synchronize()
+    _lib.check_status(0)
+
+
+def test_two_tile_rows_with_other_key_counts_and_masks(hb):
+    """More keys than query rows run in the two-tile kernel; a single row block or a causal mask falls back to
+    the row's one-tile form (row 0), so the results are those of row 0."""
+    g = torch.Generator().manual_seed(77)
+    q8 = torch.randn(2, 256, 64, generator=g).to(torch.float8_e4m3fn)
+    k8, v8 = (torch.randn(2, 400, 64, generator=g).to(torch.float8_e4m3fn) for _ in range(2))
+    vb = v8.permute(0, 2, 1)
+    blk8, blk_raw = o.fp8_attention(bits(q8), bits(k8), bits(vb), 1, 2, return_parts=True, block_n=128)
+    for config in (6, 8):
+        got = hb.fp8_attention(q8.cuda(), k8.cuda(), v8.cuda().permute(0, 2, 1), 1, 2, out_dtype=torch.float32, config=config)
+        got8 = hb.fp8_attention(q8.cuda(), k8.cuda(), v8.cuda().permute(0, 2, 1), 1, 2, config=config)
+        assert_near_bit_exact(got.cpu().numpy(), bits(got8), blk_raw, blk8)
+    for causal, rows in ((True, 256), (False, 128)):
+        a = hb.fp8_attention(q8[:, :rows].cuda(), k8.cuda(), v8.cuda().permute(0, 2, 1), 1, 2, out_dtype=torch.float32,
+                             config=7, causal=causal)
+        b = hb.fp8_attention(q8[:, :rows].cuda(), k8.cuda(), v8.cuda().permute(0, 2, 1), 1, 2, out_dtype=torch.float32,
+                             config=0, causal=causal)
+        assert torch.equal(a, b)
+    torch.cuda.synchronize()
+    _lib.check_status(0)
+
+
+@pytest.mark.parametrize("batch,heads,seq,dim", [(2, 4, 256, 64), (1, 2, 512, 128), (2, 2, 1024, 64)])
+def test_two_tile_lazy_row_stays_within_the_stated_tolerance(hb, batch, heads, seq, dim):
+    (q8, k8, v8), (qd, kd, vd) = make_inputs(batch, heads, seq, dim, seed=7, v_contiguous=False)
+    _, one_raw = o.fp8_attention(bits(q8), bits(k8), bits(v8), batch, heads, return_parts=True)
+    got = hb.fp8_attention(qd, kd, vd, batch, heads, out_dtype=torch.float32, config=10).cpu().numpy()
+    np.testing.assert_allclose(got, one_raw, rtol=2e-2, atol=2.5e-2)
 
 
 @pytest.mark.parametrize("config", [1, 2, 3])

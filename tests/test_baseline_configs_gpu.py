@@ -1,0 +1,118 @@
+"""Parity at the full sizes and value distributions of the two benchmark configurations that the other
+GPU tests only cover at reduced size:
+
+  * the LLM-MLP GEMM, K = 4096, N = 14336, M in {16, 128, 2048, 16384}: activations N(0,1), weights
+    N(0, 0.02) rescaled to max |w| = 448, column-major, bf16 and fp32 outputs -- 64-row blocks against the
+    oracle (pytorch-labs/helion examples/fp8_gemm.py:47-56 restated in oracle/fp8_oracle.py);
+  * attention B8 H32 S4096 D128 (the loop of examples/fp8_attention.py:67-101 walked 32 times per row):
+    three batch*head slices against the oracle, single-tile and at the kernel's 128-key blocks, fp32 and
+    e4m3 outputs, and batch*head shards against slices of the unsharded result.
+
+Gates (the same as for the small cases): GEMM allclose(rtol = atol = 2e-2) against the oracle's rounded
+output; relative Frobenius error against an fp32 matmul of the dequantised operands <= 1e-3 for the fp32
+output and <= 2.5e-3 for bf16 (rounding an exact result to bf16 alone costs 1.7e-3).  Attention: near
+bit-exact against the blocked oracle, allclose(2e-2, 2e-2) against the single-tile oracle.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from helion_b200 import _lib
+from oracle import fp8_oracle as o
+from test_attention_gpu import assert_near_bit_exact, bits, make_inputs, ordinal
+
+pytestmark = pytest.mark.gpu
+
+MLP_K, MLP_N = 4096, 14336
+
+
+@pytest.fixture(scope="module")
+def hb(built_library):
+    import helion_b200
+
+    _lib.reset_status(0)
+    yield helion_b200
+    torch.cuda.synchronize()
+    _lib.check_status(0)
+
+
+class TestMlpShapes:
+    @pytest.fixture(scope="class")
+    def weight(self, hb):
+        # the weight of the largest problem's draw: x differs per M (its own rows), w is the same recipe
+        _, w = o.gemm_inputs(16, MLP_N, MLP_K, seed=2, weight_like=True)
+        wf = o.e4m3_decode(o.torch_fp8_to_bits(w))  # [K, N] view of the dequantised weight
+        assert float(np.abs(wf).max()) == 448.0
+        return w, np.ascontiguousarray(wf), w.t().contiguous().cuda().t()
+
+    @pytest.mark.parametrize("m", [16, 128, 2048, 16384])
+    def test_row_blocks_match_oracle(self, hb, weight, m):
+        w, wf, wd = weight
+        g = torch.Generator().manual_seed(1000 + m)
+        x = torch.randn(m, MLP_K, generator=g).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        xd = x.cuda()
+        out16 = hb.fp8_gemm(xd, wd, out_dtype=torch.bfloat16)
+        out32 = hb.fp8_gemm(xd, wd, out_dtype=torch.float32)
+        assert tuple(out16.shape) == (m, MLP_N)
+        rows = min(64, m)
+        for r0 in sorted({0, (m // 2 // rows) * rows, m - rows}):
+            xf = o.e4m3_decode(o.torch_fp8_to_bits(x[r0:r0 + rows]))
+            exact = np.matmul(xf, wf, dtype=np.float32)  # fp32 matmul of the dequantised operands
+            want16 = o.round_to_dtype(exact, "bf16")
+            got16 = out16[r0:r0 + rows].float().cpu().numpy()
+            got32 = out32[r0:r0 + rows].cpu().numpy()
+            np.testing.assert_allclose(got16, want16, rtol=2e-2, atol=2e-2)
+            np.testing.assert_allclose(got32, exact, rtol=2e-2, atol=2e-2)
+            assert o.rel_frobenius(got32, exact) <= 1e-3
+            assert o.rel_frobenius(got16, exact) <= 2.5e-3
+        torch.cuda.synchronize()
+        _lib.check_status(0)
+
+
+class TestLongSequenceAttention:
+    """B8 H32 S4096 D128, seed 4: the default row with the balanced tile order (what the wrapper picks)."""
+
+    B, H, S, D = 8, 32, 4096, 128
+
+    @pytest.fixture(scope="class")
+    def problem(self, hb):
+        return make_inputs(self.B, self.H, self.S, self.D, seed=4, v_contiguous=False)
+
+    @pytest.fixture(scope="class")
+    def outputs(self, hb, problem):
+        _, (qd, kd, vd) = problem
+        bh = self.B * self.H
+        out8 = hb.fp8_attention(qd, kd, vd, self.B, self.H).view(bh, self.S, self.D)
+        out32 = hb.fp8_attention(qd, kd, vd, self.B, self.H, out_dtype=torch.float32).view(bh, self.S, self.D)
+        return out8, out32
+
+    @pytest.mark.parametrize("i", [0, 131, 255])
+    def test_slices_match_oracle(self, hb, problem, outputs, i):
+        (q8, k8, v8), _ = problem
+        out8, out32 = outputs
+        qb, kb, vb = bits(q8[i:i + 1]), bits(k8[i:i + 1]), bits(v8[i:i + 1])
+        one8, one_raw = o.fp8_attention(qb, kb, vb, 1, 1, return_parts=True)
+        blk8, blk_raw = o.fp8_attention(qb, kb, vb, 1, 1, return_parts=True, block_n=128)
+        got32 = out32[i].cpu().numpy()[None, None]
+        got8 = bits(out8[i])[None, None]
+        assert_near_bit_exact(got32, got8, blk_raw, blk8)
+        np.testing.assert_allclose(got32, one_raw, rtol=2e-2, atol=2e-2)
+        got8f = o.e4m3_decode(got8)
+        bad = np.abs(got8f - one8) > 2e-2 + 2e-2 * np.abs(one8)
+        assert bad.mean() <= 2e-3
+        assert (np.abs(ordinal(got8) - ordinal(o.e4m3_encode(one8)))[bad] <= 2).all()
+
+    def test_bh_shards_equal_the_unsharded_result(self, hb, problem, outputs):
+        from helion_b200.sharding import shard_range, sharded_fp8_attention
+
+        _, (qd, kd, vd) = problem
+        out8, _ = outputs
+        full = out8.view(torch.uint8)
+        for rank in (0, 4, 7):
+            lo, hi = shard_range(self.B * self.H, 8, rank)
+            part = sharded_fp8_attention(qd, kd, vd, self.B, self.H, rank=rank, world_size=8)
+            assert torch.equal(part.view(torch.uint8).reshape(hi - lo, self.S, self.D), full[lo:hi])
+        torch.cuda.synchronize()
+        _lib.check_status(0)
