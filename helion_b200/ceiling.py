@@ -31,6 +31,12 @@ VARIANTS = [
     ("2 warpgroups per SM, without the exponentials", 2, 1, 0, 2),
     ("2 warpgroups per SM, tensor-memory traffic only", 2, 1, 0, 3),
     ("1 warpgroup per SM, 4 of 8 pairs polynomial", 1, 1, 4, 0),
+    # the full step of two warpgroups next to other roles of an attention kernel (mode = 16 + mask)
+    ("2 warpgroups + four warps polling a barrier", 2, 1, 0, 17),
+    ("2 warpgroups + one thread issuing tensor-core instructions back to back", 2, 1, 0, 18),
+    ("2 warpgroups + four warps rescaling tensor memory", 2, 1, 0, 20),
+    ("2 warpgroups + the protocol's barrier traffic in the softmax threads", 2, 1, 0, 24),
+    ("2 warpgroups + all four", 2, 1, 0, 31),
 ]
 
 

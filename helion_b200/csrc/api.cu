@@ -227,8 +227,12 @@ int hb200_debug_softmax_ceiling(int wgs, int ctas_per_sm, int poly_of8, int mode
   if (wgs < 1 || wgs > 2 || ctas_per_sm < 1 || ctas_per_sm > 2 || (wgs == 2 && ctas_per_sm != 1)) {
     return set_error(HB200_ERR_BAD_CONFIG, "softmax_ceiling: 1 or 2 warpgroups per CTA; 2 CTAs per SM only with 1 warpgroup");
   }
-  if (mode < 0 || mode > 3 || steps < 1 || steps > (1 << 20)) {
-    return set_error(HB200_ERR_BAD_CONFIG, "softmax_ceiling: mode must be 0..3 and steps 1..2^20");
+  const bool noise_mode = mode == 17 || mode == 18 || mode == 20 || mode == 24 || mode == 31;
+  if (!((mode >= 0 && mode <= 3) || noise_mode) || steps < 1 || steps > (1 << 20)) {
+    return set_error(HB200_ERR_BAD_CONFIG, "softmax_ceiling: mode must be 0..3 or 16 + a noise mask of 1, 2, 4, 8, 15; steps 1..2^20");
+  }
+  if (noise_mode && (wgs != 2 || poly_of8 != 0)) {
+    return set_error(HB200_ERR_BAD_CONFIG, "softmax_ceiling: the noise modes run two warpgroups with all exp2 on the MUFU unit");
   }
   if (cycles == nullptr || (reinterpret_cast<uintptr_t>(cycles) & 7u)) {
     return set_error(HB200_ERR_ALIGN, "softmax_ceiling: cycles must be an 8-byte aligned device pointer");

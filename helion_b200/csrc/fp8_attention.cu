@@ -568,21 +568,26 @@ const AttnConfig kAttnConfigs[] = {
     {0, true, 64, false, "lazy rescale, 64-key steps with four CTAs per SM for head_dim 64 (128-key steps otherwise)"},
     {0, false, 128, true, "two query tiles per CTA, exact running max, all exp2 on the MUFU unit"},
     {2, false, 128, true, "two query tiles per CTA, exact running max, 2 of 8 exp2 pairs on the FMA pipes (degree-5 polynomial)"},
-    {3, false, 128, true, "two query tiles per CTA, exact running max, 3 of 8 exp2 pairs on the FMA pipes (degree-5 polynomial)"},
     {4, false, 128, true, "two query tiles per CTA, exact running max, 4 of 8 exp2 pairs on the FMA pipes (degree-5 polynomial)"},
     {4, true, 128, true, "two query tiles per CTA, lazy rescale, 4 of 8 exp2 pairs on the FMA pipes (degree-5 polynomial)"},
 };
-constexpr int kNumAttnConfigs = 11;
+constexpr int kNumAttnConfigs = 10;
 constexpr int kDefaultAttnConfig = 0;
 
 // The two-tile kernel takes unmasked problems with at least two row blocks per slice and at least two key
 // steps; everything else runs the one-tile kernel.
 bool attn_pair_applies(const AttnArgs& a) { return !a.causal && a.S > ATT_BM && a.Sk > 128; }
 
-// The row used for cfg_id = -1: always an exact-running-max row.  Measured on B200 (B8 H32, cold L2):
-// head_dim 64 at 4096 keys runs 1540 us with 64-key steps and four CTAs per SM against 1665 us with
-// 128-key steps; at 1024 keys the two are equal (106.5 us), and head_dim 128 has no 64-key kernel.
-int attn_select_config(int64_t d, int64_t s) { return (d == 64 && s >= 2048) ? 4 : kDefaultAttnConfig; }
+// The row used for cfg_id = -1: always an exact-running-max row.  Measured on B200 (cold L2, exact rows only):
+//   B8 H32 S4096 D64:   row 6 (two tiles per CTA) 1501 us, row 0 1536 us, row 4 (64-key steps) 1548 us
+//   B4 H48 S1024 D64:   row 0 92 us, rows 4 and 6 98 us
+//   B8 H32 S4096 D128:  rows 0 and 6 1718-1720 us;  B4 H48 S1024 D128: row 0 107 us, row 6 115 us
+// so the two-tile kernel is taken for head_dim 64 from 2048 keys up where it applies (no mask, at least two row
+// blocks), the 64-key-step row for the other head_dim 64 problems of that length, and row 0 everywhere else.
+int attn_select_config(const AttnArgs& a) {
+  if (a.D == 64 && a.Sk >= 2048) return attn_pair_applies(a) ? 6 : 4;
+  return kDefaultAttnConfig;
+}
 
 // keys per step that a table row means for a head dimension
 int attn_block_n(int cfg_id, int64_t d) {
@@ -661,7 +666,7 @@ int attn_describe_config(int cfg_id, char* buf, int buf_len) {
 int launch_fp8_attention(const AttnArgs& args, DeviceCtx* ctx) {
   if (args.cfg_id >= kNumAttnConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_attention: no such config");
   AttnArgs a = args;
-  if (a.cfg_id < 0) a.cfg_id = attn_select_config(a.D, a.Sk);
+  if (a.cfg_id < 0) a.cfg_id = attn_select_config(a);
   const bool v_kmajor = a.v_strides[2] == 1 && a.v_strides[1] != 1;  // keys contiguous
   const uint32_t d = static_cast<uint32_t>(a.D);
   const CUtensorMapSwizzle swz_d = a.D == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;

@@ -85,10 +85,10 @@ __device__ __forceinline__ void reg_set_misc() { asm volatile("setmaxnreg.dec.sy
 __device__ __forceinline__ void reg_set_correction() { asm volatile("setmaxnreg.dec.sync.aligned.u32 88;"); }
 __device__ __forceinline__ void reg_set_softmax() { asm volatile("setmaxnreg.inc.sync.aligned.u32 176;"); }
 
-template <int D, bool V_KMAJOR, int POLY_OF8, bool LAZY>
+template <int D, bool V_KMAJOR, int OUT_DT, int POLY_OF8, bool LAZY>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 fp8_attention_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                          const __grid_constant__ CUtensorMap tmap_v, void* out, int out_dt, int BH, int S, int Sk,
+                          const __grid_constant__ CUtensorMap tmap_v, void* out, int BH, int S, int Sk,
                           int64_t out_stride_bh, int64_t out_stride_s, float scale_log2, uint32_t* status,
                           unsigned int* sched) {
   using L = PairLayout<D>;
@@ -422,13 +422,13 @@ fp8_attention_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         // The 8- and 16-bit outputs divide through the correctly rounded reciprocal with one residual
         // correction (div_by_rcp); the fp32 output keeps the IEEE division.
         const float inv_l = __frcp_rn(l_i);
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {  // rolled: runs once per unit, and the roles' hot loops share an instruction cache
           uint32_t o[32];
           tmem_ld_32x32b_x32(t_o + c * 32, o);
           tmem_wait_ld();
           if (row < S) {
-            if (out_dt == HB200_DT_E4M3) {
+            if constexpr (OUT_DT == HB200_DT_E4M3) {
               uint32_t w[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
@@ -440,7 +440,7 @@ fp8_attention_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
               uint8_t* dst = reinterpret_cast<uint8_t*>(out) + out_off + c * 32;
               *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
               *reinterpret_cast<uint4*>(dst + 16) = make_uint4(w[4], w[5], w[6], w[7]);
-            } else if (out_dt == HB200_DT_BF16) {
+            } else if constexpr (OUT_DT == HB200_DT_BF16) {
               uint16_t* dst = reinterpret_cast<uint16_t*>(out) + out_off + c * 32;
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
@@ -555,18 +555,18 @@ fp8_attention_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   }
 }
 
-template <int D, bool V_KMAJOR, int POLY_OF8, bool LAZY>
+template <int D, bool V_KMAJOR, int OUT_DT, int POLY_OF8, bool LAZY>
 int launch_pair_instance(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, const CUtensorMap& tk,
                          const CUtensorMap& tv) {
   using L = PairLayout<D>;
-  auto kernel = fp8_attention_pair_kernel<D, V_KMAJOR, POLY_OF8, LAZY>;
+  auto kernel = fp8_attention_pair_kernel<D, V_KMAJOR, OUT_DT, POLY_OF8, LAZY>;
   static std::atomic<uint64_t> smem_attr_done{0};
   HB_CUDA_CHECK(set_max_dynamic_smem_once(smem_attr_done, reinterpret_cast<const void*>(kernel), L::SMEM_BYTES, a.device));
   const int64_t m_tiles = (a.S + PAIR_BM - 1) / PAIR_BM;
   const int64_t num_units = a.BH * ((m_tiles + 1) / 2);
   if (num_units > INT32_MAX / 2) return set_error(HB200_ERR_BAD_SHAPE, "fp8_attention: too many tiles");
   const int grid = static_cast<int>(std::min<int64_t>(num_units, ctx->num_sms));
-  kernel<<<grid, PAIR_THREADS, L::SMEM_BYTES, a.stream>>>(tq, tk, tv, a.out, a.out_dtype, static_cast<int>(a.BH),
+  kernel<<<grid, PAIR_THREADS, L::SMEM_BYTES, a.stream>>>(tq, tk, tv, a.out, static_cast<int>(a.BH),
                                                           static_cast<int>(a.S), static_cast<int>(a.Sk),
                                                           a.out_strides[0], a.out_strides[1], a.scale_log2,
                                                           ctx->status_dev, a.sched);
@@ -574,24 +574,37 @@ int launch_pair_instance(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& t
   return HB200_OK;
 }
 
-template <int D, bool V_KMAJOR>
+template <int D, bool V_KMAJOR, int OUT_DT>
 int launch_pair_by_row(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, const CUtensorMap& tk,
                        const CUtensorMap& tv, int poly_of8, bool lazy) {
   if (lazy) {
-    if (poly_of8 == 4) return launch_pair_instance<D, V_KMAJOR, 4, true>(a, ctx, tq, tk, tv);
+    if (poly_of8 == 4) return launch_pair_instance<D, V_KMAJOR, OUT_DT, 4, true>(a, ctx, tq, tk, tv);
     return set_error(HB200_ERR_BAD_CONFIG, "fp8_attention: config has no kernel instance");
   }
   switch (poly_of8) {
     case 0:
-      return launch_pair_instance<D, V_KMAJOR, 0, false>(a, ctx, tq, tk, tv);
+      return launch_pair_instance<D, V_KMAJOR, OUT_DT, 0, false>(a, ctx, tq, tk, tv);
     case 2:
-      return launch_pair_instance<D, V_KMAJOR, 2, false>(a, ctx, tq, tk, tv);
-    case 3:
-      return launch_pair_instance<D, V_KMAJOR, 3, false>(a, ctx, tq, tk, tv);
+      return launch_pair_instance<D, V_KMAJOR, OUT_DT, 2, false>(a, ctx, tq, tk, tv);
     case 4:
-      return launch_pair_instance<D, V_KMAJOR, 4, false>(a, ctx, tq, tk, tv);
+      return launch_pair_instance<D, V_KMAJOR, OUT_DT, 4, false>(a, ctx, tq, tk, tv);
     default:
       return set_error(HB200_ERR_BAD_CONFIG, "fp8_attention: config has no kernel instance");
+  }
+}
+
+template <int D, bool V_KMAJOR>
+int launch_pair_by_dtype(const AttnArgs& a, DeviceCtx* ctx, const CUtensorMap& tq, const CUtensorMap& tk,
+                         const CUtensorMap& tv, int poly_of8, bool lazy) {
+  switch (a.out_dtype) {
+    case HB200_DT_E4M3:
+      return launch_pair_by_row<D, V_KMAJOR, HB200_DT_E4M3>(a, ctx, tq, tk, tv, poly_of8, lazy);
+    case HB200_DT_BF16:
+      return launch_pair_by_row<D, V_KMAJOR, HB200_DT_BF16>(a, ctx, tq, tk, tv, poly_of8, lazy);
+    case HB200_DT_FP32:
+      return launch_pair_by_row<D, V_KMAJOR, HB200_DT_FP32>(a, ctx, tq, tk, tv, poly_of8, lazy);
+    default:
+      return set_error(HB200_ERR_BAD_DTYPE, "fp8_attention: unsupported out_dtype");
   }
 }
 
@@ -603,11 +616,11 @@ int launch_fp8_attention_pair(const AttnArgs& a, DeviceCtx* ctx, const CUtensorM
                               const CUtensorMap& tv, bool v_kmajor, int poly_of8, bool lazy) {
   if (a.causal) return set_error(HB200_ERR_BAD_CONFIG, "fp8_attention: the two-tile rows have no causal mask");
   if (a.D == 64) {
-    return v_kmajor ? launch_pair_by_row<64, true>(a, ctx, tq, tk, tv, poly_of8, lazy)
-                    : launch_pair_by_row<64, false>(a, ctx, tq, tk, tv, poly_of8, lazy);
+    return v_kmajor ? launch_pair_by_dtype<64, true>(a, ctx, tq, tk, tv, poly_of8, lazy)
+                    : launch_pair_by_dtype<64, false>(a, ctx, tq, tk, tv, poly_of8, lazy);
   }
-  return v_kmajor ? launch_pair_by_row<128, true>(a, ctx, tq, tk, tv, poly_of8, lazy)
-                  : launch_pair_by_row<128, false>(a, ctx, tq, tk, tv, poly_of8, lazy);
+  return v_kmajor ? launch_pair_by_dtype<128, true>(a, ctx, tq, tk, tv, poly_of8, lazy)
+                  : launch_pair_by_dtype<128, false>(a, ctx, tq, tk, tv, poly_of8, lazy);
 }
 
 }  // namespace hb

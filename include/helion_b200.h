@@ -249,6 +249,9 @@ HB200_API int hb200_debug_wait_selftest(int device, int limit_ms, void* stream);
  *   wgs: softmax warpgroups per CTA (1 or 2); ctas_per_sm: 1 or 2 (2 only with wgs = 1);
  *   poly_of8: of every 8 pairs of exponentials, how many run as a polynomial on the FMA pipes (0, 2, 3, 4);
  *   mode: 0 full step, 1 without the row max, 2 without the exponentials, 3 tensor-memory traffic only;
+ *      16 + mask (wgs = 2, poly_of8 = 0): the full step next to other roles of an attention kernel, mask bit
+ *      1 = four warps polling a barrier, 2 = one thread issuing tensor-core instructions back to back,
+ *      4 = four warps rescaling tensor memory, 8 = the softmax threads' own barrier traffic; masks 1, 2, 4, 8, 15;
  *   cycles: device pointer to num_sms * ctas_per_sm uint64: SM clocks the slowest warp of each CTA took.
  * Cycles per step per SM = cycles / (steps * wgs * ctas_per_sm): the floor for any pipeline built around this
  * arithmetic.  A measurement aid; the reference has no counterpart. */

@@ -98,17 +98,23 @@ def test_random_fp8_attention(hb, b, h, s, d, v_contig, cfg, seed):
     assert np.isfinite(got).all()
     # Against the oracle that walks the keys in the kernel's own steps: all but a few elements within 1e-3 (one P
     # element on the other side of an e4m3 rounding boundary moves its whole row), every element within 2e-2.
-    bn = 64 if d == 64 and (cfg == 4 or (cfg is None and s >= 2048)) else 128
+    bn = 64 if d == 64 and cfg == 4 else 128  # the default row walks 128-key steps for every shape drawn here
     _, blk_raw = o.fp8_attention(bits(q8), bits(k8), vbits, b, h, return_parts=True, block_n=bn)
     off = np.abs(got - blk_raw) > 1e-3 + 1e-3 * np.abs(blk_raw)
     assert off.mean() <= 2e-3
     np.testing.assert_allclose(got, blk_raw, rtol=2e-2, atol=2e-2)
-    # Against the single-tile evaluation (what ref-eager computes): the running max of a blocked walk changes how
-    # the un-normalised P rounds, which any blocked kernel shares; at most 1e-4 of the elements may leave 2e-2.
+    # The parity contract of the attention kernel is the comparison above: the reference's own loop
+    # (examples/fp8_attention.py:67-101) walked at the kernel's key-block size, every element within
+    # allclose(rtol = atol = 2e-2) and all but 0.2 % within 1e-3.  The single-tile evaluation (what ref-eager
+    # computes when the whole key range is one tile) is a different schedule of the same loop: the running max of
+    # a blocked walk changes how the un-normalised P rounds to e4m3, which the reference's compiled kernel shares
+    # with this one.  Against it a bounded excess is allowed: at most 1e-4 of a case's elements beyond 2e-2, none
+    # beyond 4e-2 (EXCESS_NOTE).
     viol = np.abs(got - one_raw) > 2e-2 + 2e-2 * np.abs(one_raw)
     assert viol.mean() <= 1e-4 and np.abs(got - one_raw).max() <= 4e-2
-    out8 = hb.fp8_attention(q8.cuda(), k8.cuda(), v_dev, b, h, config=cfg)
-    assert (out8.view(torch.uint8).cpu().numpy() == o.e4m3_encode(got)).mean() >= 0.9999
+    out8 = hb.fp8_attention(q8.cuda(), k8.cuda(), v_dev, b, h, config=cfg).view(torch.uint8).cpu().numpy()
+    assert (out8 == o.e4m3_encode(got)).mean() >= 0.9999  # the e4m3 output is the fp32 result rounded once
+    assert (out8 == o.e4m3_encode(blk_raw)).mean() >= 0.995  # and matches the blocked oracle's bytes
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
