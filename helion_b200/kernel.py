@@ -11,9 +11,8 @@ What the reference's harness does with a kernel object (pytorch-labs/helion):
   * ``.reset()``, ``.configs``, ``.fn``, ``.autotune(args)``  (benchmarks/run.py:401; kernel.py:190-279)
 
 There is no Triton here, so ``to_triton_code`` returns a description of the CUDA kernel and the
-chosen tile configuration; the autotuner is replaced by the committed tile-config table
-(``tile_table.json`` + the table inside the library), so ``autotune`` just reports the table's
-choice.  Ref-eager mode (``HELION_INTERPRET=1``) is the reference's CPU interpreter; this
+chosen tile configuration; the autotuner is replaced by the tile-config tables inside the library
+(``hb200_describe_config`` prints them), so ``autotune`` just reports the table's choice.  Ref-eager mode (``HELION_INTERPRET=1``) is the reference's CPU interpreter; this
 library has no CPU path and refuses to run in that mode rather than silently launching CUDA.
 """
 from __future__ import annotations
@@ -25,6 +24,26 @@ from typing import Any, Callable, Dict, Optional, Sequence
 import torch
 
 from . import _lib
+
+
+class ShimRefMode(str):
+    """Value of ``settings.ref_mode``.  The reference's harness tests it with
+    ``settings.ref_mode != RefMode.OFF`` (helion/runtime/ref_mode.py:41-43), where ``RefMode`` is an enum with
+    the values "off" and "eager"; this string compares equal to the enum member of the same value (and to the
+    member's name in either case), so that check works on these settings without importing helion."""
+
+    def _same(self, other: Any) -> bool:
+        value = getattr(other, "value", other)
+        return isinstance(value, str) and value.lower() == self.lower()
+
+    def __eq__(self, other: Any) -> bool:  # type: ignore[override]
+        return self._same(other)
+
+    def __ne__(self, other: Any) -> bool:  # type: ignore[override]
+        return not self._same(other)
+
+    def __hash__(self) -> int:
+        return hash(self.lower())
 
 
 @dataclass
@@ -39,7 +58,7 @@ class ShimSettings:
     force_autotune: bool = False
     use_default_config: bool = False
     print_output_code: bool = False
-    ref_mode: str = "OFF"
+    ref_mode: Any = ShimRefMode("off")
     autotune_compile_timeout: int = 60
     extra: Dict[str, Any] = field(default_factory=dict)
 
@@ -156,15 +175,16 @@ class DropInKernel:
         self._bound.clear()
 
     def __call__(self, *args: Any, **kwargs: Any) -> Any:
-        if kwargs:
-            return self._launch_fn(args, None, **kwargs)
+        if kwargs:  # keyword-only extensions (out_dtype, out, config, ...): same guard, no bind cache
+            return self._launch(args, None, **kwargs)
         return self.bind(args)(*args)
 
     # -- internals ------------------------------------------------------------------------------
-    def _launch(self, args: Sequence[Any], cfg_id: Optional[int]) -> Any:
-        if _ref_eager_requested() or str(self.settings.ref_mode).upper().endswith("EAGER"):
+    def _launch(self, args: Sequence[Any], cfg_id: Optional[int], **kwargs: Any) -> Any:
+        mode = getattr(self.settings.ref_mode, "value", self.settings.ref_mode)
+        if _ref_eager_requested() or str(mode).upper().endswith("EAGER"):
             raise RuntimeError(
                 f"{self.name}: ref-eager mode (HELION_INTERPRET=1) is the reference's CPU interpreter; "
                 "helion_b200 has no CPU path and will not silently run CUDA under that flag"
             )
-        return self._launch_fn(args, cfg_id)
+        return self._launch_fn(args, cfg_id, **kwargs)
