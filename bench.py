@@ -333,6 +333,21 @@ def main() -> None:
     # the same launch timed alone (L2 flushed by a 512 MiB write before it, one event pair per launch)
     iso = time_steps(step, 10, 0, flush, torch)
     isolated_ms = statistics.median(iso)
+    # cuBLASLt (torch._scaled_mm, the reference's GPU baseline, examples/fp8_gemm.py:61-78) timed the same two
+    # ways on the same operands, for the like-for-like fractions of the roofline object (one GPU only)
+    cublas_b2b_ms = cublas_iso_ms = None
+    if world == 1 and not args.no_extras:
+        try:
+            one = torch.tensor(1.0, device=dev)
+
+            def cublas_step(i=0):
+                r = i % REPLICAS
+                torch._scaled_mm(xs[r], ys[r], one, one, use_fast_accum=False, out_dtype=torch.bfloat16)
+
+            cublas_b2b_ms = timed_back_to_back(cublas_step, args.steps, warmup, torch, dist, dev, world)
+            cublas_iso_ms = statistics.median(time_steps(cublas_step, 10, 0, flush, torch))
+        except Exception:  # context only
+            pass
 
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region ----------
     # hb.HostGemm is the library's call for operands in host memory: every step uploads this rank's rows of x
@@ -394,7 +409,6 @@ def main() -> None:
             xb, yb = cpu_reference_inputs(CPU_SAMPLE_ROWS)
             cpu_sec = min(cpu_reference_pass(xb, yb) for _ in range(5))
             cpu_tflops = 2.0 * CPU_SAMPLE_ROWS * N * K / cpu_sec / 1e12
-        cublas = (extras.get("cublaslt_scaled_mm_8192") or {}).get("tflops")
         line = {
             "metric": METRIC,
             "value": value,
@@ -447,7 +461,10 @@ def main() -> None:
                 "peak_source": f"2 x bf16_tflops ({peaks['bf16_tflops']}) of {peaks['source']}; dense FP8 issues at twice the bf16 rate "
                                "(the file holds no FP8 figure)",
                 "frac_of_2x_bf16_sustained": achieved / (2.0 * peaks["bf16_tflops_sustained"]),
-                "frac_of_cublaslt_fp8_same_run": (achieved / cublas) if cublas else None,
+                "frac_of_cublaslt_fp8_same_run": (cublas_b2b_ms / kernel_ms) if cublas_b2b_ms else None,
+                "cublaslt_back_to_back_ms": cublas_b2b_ms,
+                "cublaslt_isolated_launch_ms": cublas_iso_ms,
+                "isolated_frac_of_cublaslt": (cublas_iso_ms / isolated_ms) if cublas_iso_ms else None,
                 "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
                 "algorithmic_flops_per_launch": shard_flops,
                 "kernel_ms": kernel_ms,

@@ -120,9 +120,51 @@ int device_init_error(int device) {
   return HB200_ERR_CUDA;
 }
 
+namespace {
+// Encoded tensor maps of this thread's recent launches: a serving loop launches the same few (pointer, shape,
+// strides, box) combinations over and over, and an encode is a driver call.  Thread-local, so re-entrant without a
+// lock; a map depends on nothing but its key (the driver encodes it on the host from these values alone).
+struct TmapKey {
+  const void* base;
+  uint64_t dims[3];
+  uint64_t strides[2];
+  uint32_t box[3];
+  int rank, dtype, swizzle;
+  bool operator==(const TmapKey& o) const { return std::memcmp(this, &o, sizeof(TmapKey)) == 0; }
+};
+struct TmapCache {
+  static constexpr int kEntries = 16;
+  TmapKey keys[kEntries];
+  CUtensorMap maps[kEntries];
+  int used = 0, next = 0;
+};
+thread_local TmapCache t_tmap_cache;
+}  // namespace
+
 int encode_tmap(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, int rank, const uint64_t* dims,
                 const uint64_t* strides, const uint32_t* box, CUtensorMapSwizzle swizzle) {
   if (g_encode_tiled == nullptr) return set_error(HB200_ERR_CUDA, "tensor-map encoder not initialised");
+  TmapKey key;
+  std::memset(&key, 0, sizeof(key));  // padding too: keys are compared as bytes
+  const bool cacheable = rank >= 1 && rank <= 3;
+  if (cacheable) {
+    key.base = base;
+    key.rank = rank;
+    key.dtype = static_cast<int>(dtype);
+    key.swizzle = static_cast<int>(swizzle);
+    for (int i = 0; i < rank; ++i) {
+      key.dims[i] = dims[i];
+      key.box[i] = box[i];
+      if (i + 1 < rank) key.strides[i] = strides[i];
+    }
+    TmapCache& c = t_tmap_cache;
+    for (int i = 0; i < c.used; ++i) {
+      if (c.keys[i] == key) {
+        *map = c.maps[i];
+        return HB200_OK;
+      }
+    }
+  }
   cuuint64_t gdims[5];
   cuuint64_t gstrides[5];
   cuuint32_t gbox[5];
@@ -143,6 +185,12 @@ int encode_tmap(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, i
                   static_cast<int>(r), rank, (unsigned long long)dims[0], (unsigned long long)(rank > 1 ? dims[1] : 0),
                   (unsigned long long)(rank > 1 ? strides[0] : 0), box[0], rank > 1 ? box[1] : 0);
     return set_error(HB200_ERR_CUDA, buf);
+  }
+  if (cacheable) {
+    TmapCache& c = t_tmap_cache;
+    const int slot = c.used < TmapCache::kEntries ? c.used++ : (c.next++ % TmapCache::kEntries);
+    c.keys[slot] = key;
+    c.maps[slot] = *map;
   }
   return HB200_OK;
 }
