@@ -620,10 +620,10 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 // epilogue warps drain the two accumulators in parallel and each accumulator is handed back on its
 // own barrier, and the producer keeps prefetching the next tile's stages meanwhile.
 // ------------------------------------------------------------------------------------------------
-template <int STAGES>
+template <int STAGES, int TILE_N = 256>
 struct Pair2Layout {
   static constexpr int A_BYTES = 256 * BK;  // 256 rows of x (two 128-row MMA operands)
-  static constexpr int B_BYTES = 128 * BK;  // 128 of the tile's 256 columns of y
+  static constexpr int B_BYTES = (TILE_N / 2) * BK;  // this CTA's half of the tile's columns of y
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   // full[ST] empty[ST] acc_full[1] acc_empty[2] drain[1]
@@ -640,15 +640,18 @@ struct Pair2Layout {
 };
 
 constexpr int PAIR2_BM = 512;
-constexpr int PAIR2_BN = 256;
 constexpr int PAIR2_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 
-template <int STAGES, bool B_MN_MAJOR, int OUT_DT, int KIND = KIND_E4M3>
+// PAIR2_BN = 224 (column-major e4m3 y only) exists for problems whose 256-wide tiles leave a round of pairs
+// partly empty: 8192 columns are 37 blocks of 224, and 2 x 37 = 74 = one tile for every CTA pair.
+template <int STAGES, bool B_MN_MAJOR, int OUT_DT, int KIND = KIND_E4M3, int PAIR2_BN = 256>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR2_THREADS, 1)
 fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_out, int M, int N, int K, int group_m,
                       uint32_t* status, EpiScale sc) {
-  using L = Pair2Layout<STAGES>;
+  using L = Pair2Layout<STAGES, PAIR2_BN>;
+  static_assert(PAIR2_BN == 256 || (PAIR2_BN == 224 && !B_MN_MAJOR && KIND == KIND_E4M3), "tile widths built");
+  static_assert(L::STAGE_BYTES % 1024 == 0 && 2 * PAIR2_BN <= L::TMEM_COLS, "swizzle alignment / tensor memory");
   constexpr int ES = KIND == KIND_E4M3 ? 1 : 2;
   constexpr int KROWS = BK / ES;
   extern __shared__ uint8_t smem_raw[];
@@ -712,7 +715,7 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
         const TileCoord tc = tile_coord(tile, m_tiles, n_tiles, group_m);
         const int row0 = tc.m_blk * PAIR2_BM + static_cast<int>(rank) * 256;
-        const int col0 = tc.n_blk * PAIR2_BN + static_cast<int>(rank) * 128;
+        const int col0 = tc.n_blk * PAIR2_BN + static_cast<int>(rank) * (PAIR2_BN / 2);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -877,8 +880,12 @@ const GemmConfig kGemmConfigs[] = {
     {128, 12, 1, false, 1, "M <= 64, column-major y: operands swapped (128 columns of y x 16/32/64 rows of x), 9-12 stages", true},
     {128, 12, 1, false, 2, "M <= 64, column-major y: operands swapped, split-K 2", true},
     {128, 12, 1, false, 4, "M <= 64, column-major y: operands swapped, split-K 4", true},
+    {448, 4, 8, true, 1, "CTA pair, 512x224x128 tiles (two accumulators), 4 stages, group_m 8: 37 column blocks per 8192 (column-major y only)"},
 };
 constexpr int kNumGemmConfigs = sizeof(kGemmConfigs) / sizeof(kGemmConfigs[0]);
+// Rows of the 512-row CTA-pair kernel carry its tile as bn = 512 (256 columns) or bn = 448 (224 columns).
+static bool is_pair2(const GemmConfig& c) { return c.pair && c.bn >= 448; }
+static int pair2_width(const GemmConfig& c) { return c.bn == 448 ? 224 : 256; }
 
 // Output tensor map for the staged epilogue: 32 x 32 element boxes, swizzled like the staging buffers.
 template <int OUT_DT>
@@ -919,10 +926,10 @@ int launch_pair_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& t
   return HB200_OK;
 }
 
-template <bool B_MN, int OUT_DT, int KIND = KIND_E4M3>
+template <bool B_MN, int OUT_DT, int KIND = KIND_E4M3, int PAIR2_BN = 256>
 int launch_pair2_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
-  using L = Pair2Layout<4>;
-  auto kernel = fp8_gemm_pair2_kernel<4, B_MN, OUT_DT, KIND>;
+  using L = Pair2Layout<4, PAIR2_BN>;
+  auto kernel = fp8_gemm_pair2_kernel<4, B_MN, OUT_DT, KIND, PAIR2_BN>;
   static std::atomic<uint64_t> smem_attr_done{0};
   HB_CUDA_CHECK(set_max_dynamic_smem_once(smem_attr_done, reinterpret_cast<const void*>(kernel), L::SMEM_BYTES, a.device));
   const int64_t m_tiles = (a.M + PAIR2_BM - 1) / PAIR2_BM;
@@ -939,15 +946,15 @@ int launch_pair2_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& 
   return HB200_OK;
 }
 
-template <bool B_MN>
+template <bool B_MN, int PAIR2_BN = 256>
 int launch_pair2_by_dtype(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, int group_m) {
   switch (a.out_dtype) {
     case HB200_DT_FP16:
-      return launch_pair2_instance<B_MN, HB200_DT_FP16>(a, ctx, ta, tb, group_m);
+      return launch_pair2_instance<B_MN, HB200_DT_FP16, KIND_E4M3, PAIR2_BN>(a, ctx, ta, tb, group_m);
     case HB200_DT_BF16:
-      return launch_pair2_instance<B_MN, HB200_DT_BF16>(a, ctx, ta, tb, group_m);
+      return launch_pair2_instance<B_MN, HB200_DT_BF16, KIND_E4M3, PAIR2_BN>(a, ctx, ta, tb, group_m);
     case HB200_DT_FP32:
-      return launch_pair2_instance<B_MN, HB200_DT_FP32>(a, ctx, ta, tb, group_m);
+      return launch_pair2_instance<B_MN, HB200_DT_FP32, KIND_E4M3, PAIR2_BN>(a, ctx, ta, tb, group_m);
     default:
       return set_error(HB200_ERR_BAD_DTYPE, "fp8_gemm: unsupported out_dtype");
   }
@@ -1046,8 +1053,8 @@ int gemm_describe_config(int cfg_id, char* buf, int buf_len) {
   const GemmConfig& c = kGemmConfigs[cfg_id];
   if (c.skinny) return std::snprintf(buf, buf_len, "gemm cfg %d: split_k=%d (%s)", cfg_id, c.splits, c.note);
   return std::snprintf(buf, buf_len, "gemm cfg %d: BM=%d BN=%d BK=128 stages=%d group_m=%d split_k=%d (%s)", cfg_id,
-                       c.bn == 512 ? 512 : (c.pair ? 256 : 128), c.bn == 512 ? 256 : c.bn, c.stages, c.group_m, c.splits,
-                       c.note);
+                       is_pair2(c) ? 512 : (c.pair ? 256 : 128), is_pair2(c) ? pair2_width(c) : c.bn, c.stages, c.group_m,
+                       c.splits, c.note);
 }
 
 size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int cfg_id) {
@@ -1058,35 +1065,39 @@ size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int 
 }
 
 // Chooses the table row with the smallest estimated time of the persistent schedule, in SM cycles:
-//   waves x (K blocks x cycles per K block / measured tensor-pipe efficiency + exposed epilogue).
-// Efficiencies are tensor-pipe-active fractions measured at 8192^3 on B200: single-CTA 128x256 0.75,
-// 128x128 0.51, 128x64 0.26.  The two CTA-pair rows are fitted to the sweep (python -m helion_b200.sweep)
-// over K = 4096 and K = 8192 problems: time per round of tiles = a * K blocks + b with the same main-loop
-// efficiency (0.88) and ~3000 cycles per tile that no overlap hides, for 256x256 and 512x256 tiles
-// alike -- so the larger tile wins whenever it does not cost an extra round.  A pair tile occupies two SMs.
+//   rounds of tiles x (K blocks x cycles per K block + exposed cycles per tile).
+// Single-CTA rows: 512 / 256 / 128 cycles per K block at full tensor rate over the tensor-pipe-active
+// fractions measured at 8192^3 (128x256: 0.75, 128x128: 0.51, 128x64: 0.26).  The CTA-pair rows are fitted
+// to launches timed back to back (20 per event pair, rows interleaved, the GPU at its power cap) on
+// K = 4096 and K = 8192 problems; per round of tiles, in microseconds at K = 8192 / K = 4096:
+//   256x256: 31.5-33.6 / 14.5-15.9    512x256: 59.8-62.6 / 29.1-32.5    512x224: 52.8-55.3 / 26.3-29.3
+// (the 512x224 round took 0.88-0.95 of a 512x256 round, depending on the GPU).  What decides between
+// them is mostly the number of rounds: 8192^3 is 7 rounds of 512x256 tiles, 8 of 512x224, 14 of 256x256;
+// its 1024-, 2048- and 4096-row shards are 1, 2, 4 rounds of 512x224 tiles (37 column blocks x 2, 4, 8 row
+// blocks on 74 CTA pairs) where 512x256 tiles leave 10, 20, 40 of 74 x rounds slots empty.
+// A pair tile occupies two SMs.  The 224-wide row is built for a column-major y only.
 static int gemm_select_config_nosplit(int64_t M, int64_t N, int64_t K, bool y_colmajor, int num_sms) {
   struct Candidate {
     int cfg;
     int64_t bm, bn;          // outputs per tile
     bool pair;
-    double cycles_per_kb;    // at full tensor rate
-    double eff;
-    double epilogue;         // exposed cycles per tile
+    double cycles_per_kb;    // per K block of one tile
+    double exposed;          // cycles per tile that no overlap hides
   };
-  const Candidate candidates[5] = {
-      {3, 128, 256, false, 512.0, 0.75, 0.0},  {1, 128, 128, false, 256.0, 0.51, 0.0},
-      {2, 128, 64, false, 128.0, 0.26, 0.0},   {6, 256, 256, true, 512.0, 0.88, 3000.0},
-      {14, 512, 256, true, 1024.0, 0.88, 3300.0},
+  const Candidate candidates[6] = {
+      {3, 128, 256, false, 512.0 / 0.75, 0.0}, {1, 128, 128, false, 256.0 / 0.51, 0.0},
+      {2, 128, 64, false, 128.0 / 0.26, 0.0},  {6, 256, 256, true, 620.0, 1500.0},
+      {14, 512, 256, true, 1100.0, 6000.0},    {21, 512, 224, true, 1012.0, 6000.0},
   };
   const double k_blocks = static_cast<double>((K + BK - 1) / BK);
   int best = 3;
   double best_cost = -1.0;
   for (const Candidate& c : candidates) {
-    if (!y_colmajor && c.bn < 128) continue;
+    if (!y_colmajor && (c.bn < 128 || c.bn == 224)) continue;
     const int64_t slots = c.pair ? num_sms / 2 : num_sms;
     const int64_t tiles = ((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
     const int64_t waves = (tiles + slots - 1) / slots;
-    const double cost = static_cast<double>(waves) * (k_blocks * c.cycles_per_kb / c.eff + c.epilogue);
+    const double cost = static_cast<double>(waves) * (k_blocks * c.cycles_per_kb + c.exposed);
     if (best_cost < 0 || cost < best_cost) {
       best_cost = cost;
       best = c.cfg;
@@ -1240,7 +1251,7 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
   if (cfg_id >= kNumGemmConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: no such config");
   const GemmConfig& c = kGemmConfigs[cfg_id];
   if (c.skinny) return launch_fp8_gemm_skinny(a, ctx, effective_splits(a.K, c.splits));
-  if (!a.y_colmajor && c.bn < 128) {
+  if (!a.y_colmajor && (c.bn < 128 || c.bn == 448)) {
     return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: this config supports column-major y only");
   }
 
@@ -1248,14 +1259,14 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(a.lda)};
-    const uint32_t box[2] = {BK, static_cast<uint32_t>(c.bn == 512 ? 256 : BM)};  // the 512x256 pair tile loads 256 rows per CTA
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(is_pair2(c) ? 256 : BM)};  // the 512-row pair tile loads 256 rows per CTA
     int rc = encode_tmap_u8(&ta, a.x, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != HB200_OK) return rc;
   }
   if (a.y_colmajor) {
     const uint64_t dims[2] = {static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.N)};
     const uint64_t strides[1] = {static_cast<uint64_t>(a.ldb)};
-    const uint32_t box[2] = {BK, static_cast<uint32_t>(c.pair ? 128 : c.bn)};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(is_pair2(c) ? pair2_width(c) / 2 : (c.pair ? 128 : c.bn))};
     int rc = encode_tmap_u8(&tb, a.y, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != HB200_OK) return rc;
   } else {
@@ -1266,6 +1277,7 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
     if (rc != HB200_OK) return rc;
   }
 
+  if (c.pair && c.bn == 448) return launch_pair2_by_dtype<false, 224>(a, ctx, ta, tb, c.group_m);
   if (c.pair && c.bn == 512) {
     return a.y_colmajor ? launch_pair2_by_dtype<false>(a, ctx, ta, tb, c.group_m)
                         : launch_pair2_by_dtype<true>(a, ctx, ta, tb, c.group_m);
@@ -1303,7 +1315,7 @@ namespace {
 
 template <int KIND, int OUT_DT, bool B_MN>
 int launch16_row(const GemmArgs& a, DeviceCtx* ctx, const GemmConfig& c, const CUtensorMap& ta, const CUtensorMap& tb) {
-  if (c.skinny || c.splits > 1 || c.bn == 64) {
+  if (c.skinny || c.splits > 1 || c.bn == 64 || c.bn == 448) {
     return set_error(HB200_ERR_BAD_CONFIG, "gemm_16bit: this table row exists for e4m3 operands only");
   }
   if (c.pair && c.bn == 512) return launch_pair2_instance<B_MN, OUT_DT, KIND>(a, ctx, ta, tb, c.group_m);
@@ -1329,7 +1341,7 @@ int launch_gemm_16bit(const GemmArgs& a, DeviceCtx* ctx) {
     // Measured at 8192^3 (bf16 / fp16, either layout of y): the 256x256 pair tile runs 768-814 us, the
     // 512x256 pair tile 786-998 us -- at half the tensor rate per byte of K its exposed epilogue no longer
     // pays for the saved operand traffic.
-    if (kGemmConfigs[cfg_id].bn == 512) cfg_id = 6;
+    if (kGemmConfigs[cfg_id].bn >= 448) cfg_id = 6;
   }
   if (cfg_id >= kNumGemmConfigs) return set_error(HB200_ERR_BAD_CONFIG, "gemm_16bit: no such config");
   const GemmConfig& c = kGemmConfigs[cfg_id];
@@ -1345,7 +1357,7 @@ int launch_gemm_16bit(const GemmArgs& a, DeviceCtx* ctx) {
   if (a.y_colmajor) {
     const uint64_t dims[2] = {static_cast<uint64_t>(a.K * ES), static_cast<uint64_t>(a.N)};
     const uint64_t strides[1] = {static_cast<uint64_t>(a.ldb * ES)};
-    const uint32_t box[2] = {BK, static_cast<uint32_t>(c.pair ? 128 : c.bn)};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(is_pair2(c) ? pair2_width(c) / 2 : (c.pair ? 128 : c.bn))};
     int rc = encode_tmap_u8(&tb, a.y, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != HB200_OK) return rc;
   } else {

@@ -104,6 +104,27 @@ def test_every_table_config_gives_the_same_result(hb):
         hb.fp8_gemm(to_dev(x), to_dev(y.contiguous()), config=2)
 
 
+@pytest.mark.parametrize("m,n,k", [(1024, 8192, 256), (1000, 8200, 384), (512, 224, 128), (2048, 14336, 128)])
+def test_224_wide_pair_tiles_equal_the_256_wide_ones(hb, m, n, k):
+    """Table row 21 (512x224 tiles, 37 column blocks per 8192 columns) walks K in the same order as row 14
+    (512x256), so every output is the same fp32 sum: the results must be bit-identical, clipped last column
+    block (8192 = 36 x 224 + 128) and ragged rows included; the row is refused for a row-major y."""
+    from helion_b200 import _lib
+
+    assert "512x224" in _lib.describe_config(_lib.OP_GEMM, 21)
+    x, y = o.gemm_inputs(m, n, k, seed=2100 + m + n)
+    xd, yd = to_dev(x), to_dev(y)
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        wide = hb.fp8_gemm(xd, yd, out_dtype=dt, config=14)
+        narrow = hb.fp8_gemm(xd, yd, out_dtype=dt, config=21)
+        assert torch.equal(wide, narrow), f"{m}x{n}x{k} {dt}"
+    if m * n <= 1 << 20:
+        check_against_oracle(hb, x, y, torch.float32, config=21)
+    if n % 16 == 0:
+        with pytest.raises(ValueError, match="column-major y only"):
+            hb.fp8_gemm(xd, to_dev(y.contiguous()), config=21)
+
+
 @pytest.mark.parametrize("m,n,k", [(16, 512, 1024), (16, 14336, 4096), (128, 1024, 2048), (100, 272, 1152)])
 @pytest.mark.parametrize("colmajor", [True, False], ids=["y_colmajor", "y_rowmajor"])
 def test_split_k_configs_match_oracle(hb, m, n, k, colmajor):

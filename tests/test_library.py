@@ -105,6 +105,12 @@ def test_select_config_prefers_wide_tiles_for_big_problems(built_library):
     assert 0 <= small < _lib.num_configs(_lib.OP_GEMM)
     # 128x64 tiles are only built for column-major y
     assert lib.hb200_fp8_gemm_select_config(128, 2048, 256, 0, _lib.DT_FP16) in (0, 1)
+    # row shards of the 8192^3 problem: 37 column blocks of 224 give every CTA pair a tile where 32 blocks of
+    # 256 leave pairs idle; the whole problem keeps the wider tile (7 rounds against 8); row-major y has no 224 row
+    for rows in (1024, 2048, 4096):
+        assert "512x224" in _lib.describe_config(_lib.OP_GEMM, lib.hb200_fp8_gemm_select_config(rows, 8192, 8192, 1, _lib.DT_BF16))
+        assert "512x224" not in _lib.describe_config(_lib.OP_GEMM, lib.hb200_fp8_gemm_select_config(rows, 8192, 8192, 0, _lib.DT_BF16))
+    assert "512x256" in _lib.describe_config(_lib.OP_GEMM, big)
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
