@@ -100,18 +100,23 @@ class ClockSampler:
         }
         get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(
             nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        power = 0.0
+        n = 0
         while not self._stop.is_set():
             try:
                 sm = float(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
-                power = nv.nvmlDeviceGetPowerUsage(self._handle) / 1000.0
-                mask = int(get_reasons(self._handle))
+                if n % 4 == 0:  # a short timed region leaves room for few queries: the clock first, the rest less often
+                    power = nv.nvmlDeviceGetPowerUsage(self._handle) / 1000.0
+                    mask = int(get_reasons(self._handle))
+                    for name, bit in names.items():
+                        if mask & bit:
+                            self.reasons.add(name)
                 self.samples.append((power, sm))
-                for name, bit in names.items():
-                    if mask & bit:
-                        self.reasons.add(name)
+                n += 1
             except Exception:
                 pass
-            time.sleep(self.period_s)
+            if self.period_s >= 0.001:
+                time.sleep(self.period_s)
 
     def stop(self) -> dict:
         if self._nvml is None:
