@@ -1,9 +1,12 @@
 """Builds the C-ABI shared library (``helion_b200/_C/libhelion_b200.so``) with nvcc for sm_100a.
 
     python -m helion_b200.build [--force] [--verbose]
+    python -m helion_b200.build --define HB_SKINNY_TRACE --output helion_b200/_C/libhelion_b200_trace.so
 
 The library is built in-tree so that it travels with the source tree; it is rebuilt only when a
-source file is newer than the existing binary.  nvcc cross-compiles without a GPU.
+source file is newer than the existing binary.  nvcc cross-compiles without a GPU.  ``--define`` /
+``--output`` build a second, instrumented copy beside it (development aids such as the phase stamps of
+``python -m helion_b200.chain_trace``); the product library is never built with a define.
 """
 from __future__ import annotations
 
@@ -52,17 +55,27 @@ def _stale() -> bool:
     return any(p.stat().st_mtime > built for p in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every CUDA source for sm_100a and link the shared library; returns its path."""
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, defines: tuple = (), output: Path | None = None) -> Path:
+    """Compile every CUDA source for sm_100a and link the shared library; returns its path.
+
+    With ``defines`` the objects go to a directory of their own and the library to ``output``."""
+    variant = bool(defines) or output is not None
+    if variant and output is None:
+        raise ValueError("an instrumented build needs its own output path")
+    lib_path = Path(output).resolve() if variant else LIB_PATH
+    if lib_path == LIB_PATH and variant:
+        raise ValueError("the product library is not built with extra defines")
+    if not variant and not force and not _stale():
         return LIB_PATH
     nvcc = find_nvcc()
     OUT_DIR.mkdir(exist_ok=True)
+    obj_dir = OUT_DIR / ("variant_" + "_".join(defines)) if variant else OUT_DIR
+    obj_dir.mkdir(exist_ok=True)
     objs = []
     procs = []
     for src in SOURCES:
-        obj = OUT_DIR / (src + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(INCLUDE_DIR), "-c", str(CSRC / src), "-o", str(obj)]
+        obj = obj_dir / (src + ".o")
+        cmd = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-I", str(INCLUDE_DIR), "-c", str(CSRC / src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -78,22 +91,25 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             failed.append(src)
     if failed:
         raise RuntimeError(f"nvcc failed for: {', '.join(failed)}")
-    tmp = OUT_DIR / "libhelion_b200.so.tmp"
+    tmp = lib_path.with_suffix(".so.tmp")
     link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC", *objs, "-o", str(tmp)]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         sys.stdout.write(r.stdout)
         raise RuntimeError("link failed")
-    os.replace(tmp, LIB_PATH)
-    return LIB_PATH
+    os.replace(tmp, lib_path)
+    return lib_path
 
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="print nvcc commands and ptxas resource usage")
+    ap.add_argument("--define", action="append", default=[], metavar="NAME", help="instrumented build: -DNAME (needs --output)")
+    ap.add_argument("--output", default=None, help="instrumented build: path of the library to write")
     args = ap.parse_args()
-    print(build(force=args.force, verbose=args.verbose))
+    print(build(force=args.force, verbose=args.verbose, defines=tuple(args.define),
+                output=Path(args.output) if args.output else None))
 
 
 if __name__ == "__main__":

@@ -856,6 +856,7 @@ struct GemmConfig {
   int splits;    // split-K factor (needs a workspace of splits x M x N floats when > 1)
   const char* note;
   bool skinny = false;  // operand-swapped kernel for M <= 64, column-major y (fp8_gemm_skinny.cu)
+  int skinny_mode = 0;  // 0: deepest ring, one CTA per SM; 1: half the stages, two CTAs per SM; 2: as 1, y requested before the predecessor ends
 };
 
 const GemmConfig kGemmConfigs[] = {
@@ -881,6 +882,8 @@ const GemmConfig kGemmConfigs[] = {
     {128, 12, 1, false, 2, "M <= 64, column-major y: operands swapped, split-K 2", true},
     {128, 12, 1, false, 4, "M <= 64, column-major y: operands swapped, split-K 4", true},
     {448, 4, 8, true, 1, "CTA pair, 512x224x128 tiles (two accumulators), 4 stages, group_m 8: 37 column blocks per 8192 (column-major y only)"},
+    {128, 6, 1, false, 1, "M <= 64, column-major y: operands swapped, 4-6 stages so that the CTAs of consecutive launches share an SM", true, 1},
+    {128, 6, 1, false, 1, "M <= 64, column-major y: operands swapped, 4-6 stages, y requested before the preceding kernel on the stream has ended (the caller vouches that that kernel does not write y: a weight matrix)", true, 2},
 };
 constexpr int kNumGemmConfigs = sizeof(kGemmConfigs) / sizeof(kGemmConfigs[0]);
 // Rows of the 512-row CTA-pair kernel carry its tile as bn = 512 (256 columns) or bn = 448 (224 columns).
@@ -1250,7 +1253,7 @@ int launch_fp8_gemm(const GemmArgs& a, DeviceCtx* ctx) {
   }
   if (cfg_id >= kNumGemmConfigs) return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: no such config");
   const GemmConfig& c = kGemmConfigs[cfg_id];
-  if (c.skinny) return launch_fp8_gemm_skinny(a, ctx, effective_splits(a.K, c.splits));
+  if (c.skinny) return launch_fp8_gemm_skinny(a, ctx, effective_splits(a.K, c.splits), c.skinny_mode);
   if (!a.y_colmajor && (c.bn < 128 || c.bn == 448)) {
     return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: this config supports column-major y only");
   }

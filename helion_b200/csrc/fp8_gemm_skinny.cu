@@ -16,12 +16,47 @@
 //
 // Work units are (128-column block of y, K range); with splits > 1 every unit writes fp32 partial
 // sums and the ordered reduction kernel of the general GEMM finishes the job.
+//
+// MODE 0: as many stages as shared memory holds (12 / 11 / 9), one CTA per SM.
+// MODE 1: half the stages (6 / 5 / 4), so that the CTAs of two consecutive launches fit on one SM: in a
+//         chain of launches with programmatic dependent launch the next kernel's CTAs are resident, set
+//         up and waiting when their predecessor ends, instead of being scheduled then.
+// MODE 2: MODE 1, and the producer requests its first stages of y BEFORE it waits for the predecessor
+//         (x is still read after the wait, out written after it).  Only for a y that the preceding
+//         kernel on the stream does not write -- a weight matrix in a decode loop; the caller says so by
+//         choosing the table row.  The weight stream then runs across the boundary between two layers.
+//         (Also asking for the rest of the panel to be prefetched into the L2 at that point, with evict-first
+//         loads into shared memory, was measured and dropped: 26 prefetch requests per CTA took 4-9 us to issue
+//         and the later loads were no faster -- 17.4 us per layer against 14.6.)
 #include <algorithm>
 #include <string>
 
 #include "common.cuh"
 #include "host.h"
 #include "epilogue.cuh"
+
+// Build with -DHB_SKINNY_TRACE to record, per CTA, wall-clock (globaltimer) and SM-clock stamps of the kernel's
+// phases (a development aid; hb200_debug_skinny_trace copies them to the host).  Product builds compile none of it.
+#ifdef HB_SKINNY_TRACE
+namespace hb {
+__device__ unsigned long long g_skinny_trace[8192][12];
+__shared__ unsigned long long sk_prod[4];  // the producer thread's stamps
+__device__ unsigned int g_skinny_trace_n;
+__device__ __forceinline__ unsigned long long sk_gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+}
+extern "C" __attribute__((visibility("default"))) int hb200_debug_skinny_trace(unsigned long long* host_dst, unsigned int* n) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_dst, hb::g_skinny_trace, sizeof(unsigned long long) * 8192 * 12);
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(n, hb::g_skinny_trace_n, sizeof(unsigned int));
+  return static_cast<int>(e);
+}
+#define SK_STAMP(slot) do { sk_t[slot] = hb::sk_gtime(); } while (0)
+#else
+#define SK_STAMP(slot) do { } while (0)
+#endif
 
 namespace hb {
 
@@ -34,12 +69,13 @@ constexpr int SK_EPI_THREADS = 128;
 constexpr int SK_ACC_STRIDE = 64;  // tensor-memory columns between the two accumulators
 constexpr int SK_TMEM_COLS = 128;
 
-template <int NM>
+template <int NM, int MODE>
 struct SkinnyLayout {
   static constexpr int W_BYTES = SK_BN * SK_BK;
   static constexpr int X_BYTES = NM * SK_BK;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
-  static constexpr int STAGES = NM == 16 ? 12 : (NM == 32 ? 11 : 9);
+  static constexpr int DEEP_STAGES = NM == 16 ? 12 : (NM == 32 ? 11 : 9);
+  static constexpr int STAGES = MODE == 0 ? DEEP_STAGES : (NM == 16 ? 6 : (NM == 32 ? 5 : 4));  // modes 1, 2
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   // full[STAGES] empty[STAGES] acc_full[2] acc_empty[2] drain[1]
   static constexpr int NUM_BARS = 2 * STAGES + 5;
@@ -47,14 +83,15 @@ struct SkinnyLayout {
   static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = MISC_OFFSET + 16 + 1024;
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of the swizzle atoms");
-  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+  static_assert(SMEM_BYTES <= (MODE == 0 ? 227 : 113) * 1024, "shared memory budget (two CTAs per SM in modes 1 and 2)");
 };
 
-template <int NM, int OUT_DT>
-__global__ void __launch_bounds__(SK_THREADS, 1)
+template <int NM, int OUT_DT, int MODE>
+__global__ void __launch_bounds__(SK_THREADS, MODE == 0 ? 1 : 2)
 fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, void* out,
                        int M, int N, int K, int64_t ldc, uint32_t* status, int splits, float* partials, EpiScale sc) {
-  using L = SkinnyLayout<NM>;
+  using L = SkinnyLayout<NM, MODE>;
+  constexpr bool EARLY_Y = MODE == 2;
   constexpr int STAGES = L::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -74,6 +111,10 @@ fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   const int kb_per_split = (k_blocks + splits - 1) / splits;
   const int num_units = n_tiles * splits;  // unit u = (column block u % n_tiles, K range u / n_tiles)
   const WaitCtx wctx{abort_flag, status};
+#ifdef HB_SKINNY_TRACE
+  unsigned long long sk_t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  SK_STAMP(0);  // entry
+#endif
 
   if (threadIdx.x == 0) {
     // descriptor fetches overlap the barrier set-up and the tensor-memory allocation
@@ -101,7 +142,11 @@ fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   // everything above overlapped the previous kernel's tail (launch_pdl); global memory from here on
-  pdl_wait();
+  // (with EARLY_Y the producer warp does not wait here -- a thread cannot run ahead of a warp that is parked in
+  // the wait; its one working thread waits by itself after it has requested its first stages of y)
+  SK_STAMP(1);  // set-up done
+  if (!(EARLY_Y && warp == 0)) pdl_wait();
+  SK_STAMP(2);  // predecessor ended
   pdl_launch_dependents();
 
   if (warp == 0) {
@@ -109,11 +154,41 @@ fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      int prefetched = 0;  // K blocks of this CTA's first unit requested before the main loop
+      if constexpr (EARLY_Y) {
+        if (static_cast<int>(blockIdx.x) < num_units) {
+          const int split = blockIdx.x / n_tiles;
+          const int n_blk = blockIdx.x - split * n_tiles;
+          const int kb_begin = split * kb_per_split;
+          const int kb_end = min(k_blocks, kb_begin + kb_per_split);
+          prefetched = min(STAGES, kb_end - kb_begin);
+          for (int j = 0; j < prefetched; ++j) {  // fresh stages: nothing to wait for
+            mbar_arrive_expect_tx(&full[j], L::STAGE_BYTES);
+            tma_load_2d(smem + j * L::STAGE_BYTES, &tmap_w, &full[j], (kb_begin + j) * SK_BK, n_blk * SK_BN);
+          }
+#ifdef HB_SKINNY_TRACE
+          sk_prod[0] = hb::sk_gtime();
+#endif
+          pdl_wait();  // x may be the predecessor's output
+#ifdef HB_SKINNY_TRACE
+          sk_prod[1] = hb::sk_gtime();
+#endif
+          for (int j = 0; j < prefetched; ++j) {
+            tma_load_2d(smem + j * L::STAGE_BYTES + L::W_BYTES, &tmap_x, &full[j], (kb_begin + j) * SK_BK, 0);
+          }
+#ifdef HB_SKINNY_TRACE
+          sk_prod[2] = hb::sk_gtime();
+#endif
+          it = static_cast<uint32_t>(prefetched);
+        } else {
+          pdl_wait();
+        }
+      }
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
         const int split = unit / n_tiles;
         const int n_blk = unit - split * n_tiles;
-        const int kb_begin = split * kb_per_split;
-        const int kb_end = min(k_blocks, kb_begin + kb_per_split);
+        const int kb_begin = split * kb_per_split + (unit == static_cast<int>(blockIdx.x) ? prefetched : 0);
+        const int kb_end = min(k_blocks, split * kb_per_split + kb_per_split);
         for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -160,6 +235,11 @@ fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
             ok = false;
             break;
           }
+#ifdef HB_SKINNY_TRACE
+          if (it == 0) SK_STAMP(3);                                  // first stage landed
+          if (it == static_cast<uint32_t>(STAGES)) SK_STAMP(4);      // first refilled stage landed
+          if (kb == kb_end - 1) SK_STAMP(5);                         // last stage landed
+#endif
           tc_fence_after_sync();
           const uint32_t w_addr = smem_u32(smem + s * L::STAGE_BYTES);
           const uint32_t x_addr = w_addr + L::W_BYTES;
@@ -242,16 +322,27 @@ fp8_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   // ------------------------------- teardown ----------------------------------------------------
   tc_fence_before_sync();
   __syncthreads();
+#ifdef HB_SKINNY_TRACE
+  if (threadIdx.x == 32) {  // the MMA thread holds the stamps; the epilogue warps have stored their outputs by now
+    SK_STAMP(6);
+    const unsigned int idx = atomicAdd(&g_skinny_trace_n, 1u) % 8192u;
+    unsigned int smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    sk_t[7] = (static_cast<unsigned long long>(blockIdx.x) << 32) | smid;
+    for (int i = 0; i < 8; ++i) g_skinny_trace[idx][i] = sk_t[i];
+    for (int i = 0; i < 3; ++i) g_skinny_trace[idx][8 + i] = sk_prod[i];
+  }
+#endif
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc(tmem_base, SK_TMEM_COLS);
   }
 }
 
-template <int NM, int OUT_DT>
+template <int NM, int OUT_DT, int MODE>
 int launch_skinny_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, int splits) {
-  using L = SkinnyLayout<NM>;
-  auto kernel = fp8_gemm_skinny_kernel<NM, OUT_DT>;
+  using L = SkinnyLayout<NM, MODE>;
+  auto kernel = fp8_gemm_skinny_kernel<NM, OUT_DT, MODE>;
   static std::atomic<uint64_t> smem_attr_done{0};
   HB_CUDA_CHECK(set_max_dynamic_smem_once(smem_attr_done, reinterpret_cast<const void*>(kernel), L::SMEM_BYTES, a.device));
   const int64_t n_tiles = (a.N + SK_BN - 1) / SK_BN;
@@ -262,17 +353,31 @@ int launch_skinny_instance(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap&
   return HB200_OK;
 }
 
-template <int NM>
+template <int NM, int MODE>
 int launch_skinny_by_dtype(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, int splits) {
   switch (a.out_dtype) {
     case HB200_DT_FP16:
-      return launch_skinny_instance<NM, HB200_DT_FP16>(a, ctx, tw, tx, splits);
+      return launch_skinny_instance<NM, HB200_DT_FP16, MODE>(a, ctx, tw, tx, splits);
     case HB200_DT_BF16:
-      return launch_skinny_instance<NM, HB200_DT_BF16>(a, ctx, tw, tx, splits);
+      return launch_skinny_instance<NM, HB200_DT_BF16, MODE>(a, ctx, tw, tx, splits);
     case HB200_DT_FP32:
-      return launch_skinny_instance<NM, HB200_DT_FP32>(a, ctx, tw, tx, splits);
+      return launch_skinny_instance<NM, HB200_DT_FP32, MODE>(a, ctx, tw, tx, splits);
     default:
       return set_error(HB200_ERR_BAD_DTYPE, "fp8_gemm: unsupported out_dtype");
+  }
+}
+
+template <int NM>
+int launch_skinny_by_mode(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, int splits, int mode) {
+  switch (mode) {
+    case 0:
+      return launch_skinny_by_dtype<NM, 0>(a, ctx, tw, tx, splits);
+    case 1:
+      return launch_skinny_by_dtype<NM, 1>(a, ctx, tw, tx, splits);
+    case 2:
+      return launch_skinny_by_dtype<NM, 2>(a, ctx, tw, tx, splits);
+    default:
+      return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: unknown mode of the few-row kernel");
   }
 }
 
@@ -280,7 +385,7 @@ int launch_skinny_by_dtype(const GemmArgs& a, DeviceCtx* ctx, const CUtensorMap&
 
 bool gemm_skinny_supported(int64_t M, bool y_colmajor) { return y_colmajor && M >= 1 && M <= 64; }
 
-int launch_fp8_gemm_skinny(const GemmArgs& a, DeviceCtx* ctx, int splits) {
+int launch_fp8_gemm_skinny(const GemmArgs& a, DeviceCtx* ctx, int splits, int mode) {
   if (!gemm_skinny_supported(a.M, a.y_colmajor)) {
     return set_error(HB200_ERR_BAD_CONFIG, "fp8_gemm: the skinny rows need M <= 64 and a column-major y");
   }
@@ -310,13 +415,13 @@ int launch_fp8_gemm_skinny(const GemmArgs& a, DeviceCtx* ctx, int splits) {
   int rc;
   switch (nm) {
     case 16:
-      rc = launch_skinny_by_dtype<16>(a, ctx, tw, tx, splits);
+      rc = launch_skinny_by_mode<16>(a, ctx, tw, tx, splits, mode);
       break;
     case 32:
-      rc = launch_skinny_by_dtype<32>(a, ctx, tw, tx, splits);
+      rc = launch_skinny_by_mode<32>(a, ctx, tw, tx, splits, mode);
       break;
     default:
-      rc = launch_skinny_by_dtype<64>(a, ctx, tw, tx, splits);
+      rc = launch_skinny_by_mode<64>(a, ctx, tw, tx, splits, mode);
       break;
   }
   if (rc != HB200_OK) return rc;

@@ -125,7 +125,7 @@ size_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int out_dtype, int 
 // The operand-swapped kernel for M <= 64 and column-major y (fp8_gemm_skinny.cu); splits > 1 writes
 // fp32 partial sums to args.workspace and runs the ordered reduction.
 bool gemm_skinny_supported(int64_t M, bool y_colmajor);
-int launch_fp8_gemm_skinny(const GemmArgs& args, DeviceCtx* ctx, int splits);
+int launch_fp8_gemm_skinny(const GemmArgs& args, DeviceCtx* ctx, int splits, int mode);
 // out = cast(sum over splits of workspace[split][M][N]), in split order.
 int launch_splitk_reduce(const GemmArgs& args, int splits);
 

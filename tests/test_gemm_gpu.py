@@ -161,6 +161,8 @@ def test_few_rows_of_x_use_the_operand_swapped_kernel(hb, m, n, k):
         general = hb.fp8_gemm(xd, yd, out_dtype=dt, config=1)
         swapped = hb.fp8_gemm(xd, yd, out_dtype=dt, config=18)
         assert torch.equal(general, swapped), f"{m}x{n}x{k} {dt}"
+        for shallow in (22, 23):  # the same kernel with 4-6 stages / with y requested before the predecessor ends
+            assert torch.equal(general, hb.fp8_gemm(xd, yd, out_dtype=dt, config=shallow)), f"{m}x{n}x{k} {dt} row {shallow}"
     check_against_oracle(hb, x, y, torch.bfloat16, config=18)
     for cfg in (19, 20, None):
         check_against_oracle(hb, x, y, torch.float32, config=cfg)
@@ -170,6 +172,47 @@ def test_few_rows_of_x_use_the_operand_swapped_kernel(hb, m, n, k):
     if n % 16 == 0:  # (a row-major y needs N % 16 == 0 to begin with)
         with pytest.raises(ValueError, match="column-major"):  # these rows are not built for a row-major y
             hb.fp8_gemm(xd, to_dev(y.contiguous()), config=18)
+
+
+@pytest.mark.parametrize("row", [22, 23])
+def test_few_row_kernels_in_a_chain_of_launches(hb, row):
+    """Rows 22 / 23 exist for chains of launches (a decode loop): the next kernel's CTAs are resident while
+    their predecessor runs, and with row 23 they request their first stages of y before it has ended.  Here
+    every launch of the chain reads the x that the launch before it consumed and writes the out buffer the
+    launch before it wrote (the stream order the kernels must keep), against 12 different weights; each
+    result must equal the deep-ring row 18 run alone."""
+    g = torch.Generator().manual_seed(31)
+    m, n, k = 16, 1536, 2048
+    x = torch.randn(m, k, generator=g).to(torch.float8_e4m3fn).cuda()
+    ws = [torch.randn(n, k, generator=g).to(torch.float8_e4m3fn).cuda().t() for _ in range(12)]
+    want = [hb.fp8_gemm(x, w, out_dtype=torch.bfloat16, config=18) for w in ws]
+    torch.cuda.synchronize()
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    kept = []
+    for w in ws:  # back to back, no synchronisation: every launch overwrites `out` after the copy before it
+        hb.fp8_gemm(x, w, out_dtype=torch.bfloat16, out=out, config=row)
+        kept.append(out.clone())
+    torch.cuda.synchronize()
+    for i, (got, ref) in enumerate(zip(kept, want)):
+        assert torch.equal(got, ref), f"launch {i} of the chain, row {row}"
+    # the same chain replayed from a CUDA graph
+    graph_out = torch.empty(len(ws), m, n, dtype=torch.bfloat16, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i, w in enumerate(ws):
+            hb.fp8_gemm(x, w, out_dtype=torch.bfloat16, out=graph_out[i], config=row)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i, w in enumerate(ws):
+            hb.fp8_gemm(x, w, out_dtype=torch.bfloat16, out=graph_out[i], config=row)
+    graph_out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    for i, ref in enumerate(want):
+        assert torch.equal(graph_out[i], ref), f"graph launch {i}, row {row}"
 
 
 @pytest.mark.parametrize(
