@@ -647,6 +647,14 @@ def make_workload(name: str, torch, dev, hb, config=None):
         outg = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         return (lambda: hb.fp8_gemm(xa, ya, out_dtype=torch.bfloat16, out=outg, config=config),
                 GEMM_FLOPS, M * K + K * N + 2 * M * N)
+    if name.startswith("gemm_shard_"):  # one rank's rows of the 8192^3 product: gemm_shard_1024 / _2048 / _4096
+        rows = int(name[len("gemm_shard_"):])
+        g = torch.Generator(device=dev).manual_seed(1)
+        xa = torch.randn(rows, K, device=dev, generator=g).to(torch.float8_e4m3fn)
+        ya = torch.randn(N, K, device=dev, generator=g).to(torch.float8_e4m3fn).t()
+        outg = torch.empty(rows, N, dtype=torch.bfloat16, device=dev)
+        return (lambda: hb.fp8_gemm(xa, ya, out_dtype=torch.bfloat16, out=outg, config=config),
+                2.0 * rows * N * K, rows * K + K * N + 2 * rows * N)
     if name == "cublaslt_8192":  # context only: torch._scaled_mm on the same workload
         g = torch.Generator(device=dev).manual_seed(1)
         xa = torch.randn(M, K, device=dev, generator=g).to(torch.float8_e4m3fn)
@@ -711,7 +719,7 @@ PREPROCESS = [f"preprocess_{n[len('attn_'):]}" for n in ATTN_SHAPES]
 ATTN16 = [f"attn_bf16_{n[len('attn_'):]}" for n in ATTN_SHAPES]
 SDPA16 = [f"sdpa_bf16_{n[len('attn_'):]}" for n in ATTN_SHAPES]
 CAUSAL = [f"attn_causal_{n[len('attn_'):]}" for n in ATTN_SHAPES]
-WORKLOADS = ["gemm_8192", *ATTN_SHAPES, *CAUSAL, *ATTN16, *SDPA16, *(f"mlp_M{m}" for m in MLP_M), "cublaslt_8192", "gemm_8192_rowwise_scaled",
+WORKLOADS = ["gemm_8192", "gemm_shard_1024", "gemm_shard_2048", "gemm_shard_4096", *ATTN_SHAPES, *CAUSAL, *ATTN16, *SDPA16, *(f"mlp_M{m}" for m in MLP_M), "cublaslt_8192", "gemm_8192_rowwise_scaled",
              "matmul_bf16_8192", *PREPROCESS]
 
 
