@@ -114,10 +114,14 @@ struct StagedStore {
   static constexpr int NBUF = OUT32 ? 1 : 2;  // 4 KB per warp either way
 
   __device__ static __forceinline__ void store(const uint32_t (&r)[32], uint8_t* stage, uint32_t chunk_count, int lane,
-                                               const CUtensorMap* tmap_out, int col, int row0, bool inside) {
+                                               const CUtensorMap* tmap_out, int col, int row0, bool inside,
+                                               unsigned long long* trace = nullptr) {
     uint8_t* buf = stage + (chunk_count % NBUF) * STG_BYTES;
     if (lane == 0) tma_store_wait_read<NBUF - 1>();
     __syncwarp();
+#ifdef HB_GEMM_TRACE
+    if (trace != nullptr) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(trace[0]));
+#endif
     // 16-byte chunk j of row r lives at chunk j ^ ((r >> 1) & 3) (64-byte rows, SWIZZLE_64B) or
     // j ^ (r & 7) (128-byte rows, SWIZZLE_128B): the pattern the output tensor map expects
     const uint32_t swz = OUT32 ? static_cast<uint32_t>(lane & 7) : static_cast<uint32_t>((lane >> 1) & 3);
@@ -620,6 +624,32 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 // epilogue warps drain the two accumulators in parallel and each accumulator is handed back on its
 // own barrier, and the producer keeps prefetching the next tile's stages meanwhile.
 // ------------------------------------------------------------------------------------------------
+// Build with -DHB_GEMM_TRACE to record wall-clock stamps of the 512-row pair kernel's phases per leader CTA
+// (a development aid; hb200_debug_gemm_trace copies them to the host).  Product builds compile none of it.
+#ifdef HB_GEMM_TRACE
+}  // namespace
+}  // namespace hb
+namespace hb {
+__device__ unsigned long long g_gemm_trace[8192][32];
+__device__ unsigned int g_gemm_trace_n;
+__device__ __forceinline__ unsigned long long gm_gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+}  // namespace hb
+extern "C" __attribute__((visibility("default"))) int hb200_debug_gemm_trace(unsigned long long* host_dst, unsigned int* n) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_dst, hb::g_gemm_trace, sizeof(unsigned long long) * 8192 * 32);
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(n, hb::g_gemm_trace_n, sizeof(unsigned int));
+  return static_cast<int>(e);
+}
+namespace hb {
+namespace {
+#define GM_STAMP(slot) do { gm_t[slot] = hb::gm_gtime(); } while (0)
+#else
+#define GM_STAMP(slot) do { } while (0)
+#endif
+
 template <int STAGES, int TILE_N = 256>
 struct Pair2Layout {
   static constexpr int A_BYTES = 256 * BK;  // 256 rows of x (two 128-row MMA operands)
@@ -676,6 +706,12 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const int num_tiles = m_tiles * n_tiles;
   const int k_blocks = (K + BK - 1) / BK;
   const WaitCtx wctx{abort_flag, status};
+#ifdef HB_GEMM_TRACE
+  unsigned long long gm_t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  __shared__ unsigned long long gm_epi[2];
+  __shared__ unsigned long long gm_chunk[24];  // per chunk of warp 2's first tile: scores loaded, staging buffer free, store issued
+  GM_STAMP(0);  // entry
+#endif
 
   if (threadIdx.x == 0) {
     // descriptor fetches overlap the barrier set-up and the tensor-memory allocation
@@ -704,7 +740,9 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   // everything above may overlap the previous kernel's tail (launch_pdl); global memory from here on
+  GM_STAMP(1);  // set-up done
   pdl_wait();
+  GM_STAMP(2);  // predecessor ended
   pdl_launch_dependents();
 
   if (warp == 0) {
@@ -760,6 +798,10 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             ok = false;
             break;
           }
+#ifdef HB_GEMM_TRACE
+          if (it == 0) GM_STAMP(3);                                   // first operands landed
+          if (tile_iter == 0 && kb == k_blocks - 1) GM_STAMP(4);      // last operands of the first tile landed
+#endif
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + s * L::STAGE_BYTES);
           const uint32_t b_addr = a_addr + L::A_BYTES;
@@ -816,6 +858,9 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       bool ok = mbar_wait(acc_full, tile_iter & 1u, wctx, SITE_GEMM_ACC_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+#ifdef HB_GEMM_TRACE
+      if (threadIdx.x == 64 && tile_iter == 0) gm_epi[0] = hb::gm_gtime();  // first tile's accumulators complete
+#endif
       tc_fence_after_sync();
       const int row0 = tc.m_blk * PAIR2_BM + static_cast<int>(rank) * 256 + acc * 128 + quarter * 32;
       const uint32_t t_row = tmem_base + acc * PAIR2_BN + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -826,11 +871,22 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         tmem_wait_ld();
         const int col = tc.n_blk * PAIR2_BN + c;
         scale_chunk(r, sc, row0 + lane, M, col, N);
+#ifdef HB_GEMM_TRACE
+        const bool tr = threadIdx.x == 64 && tile_iter == 0 && c < 256;
+        if (tr) gm_chunk[(c / 32) * 3] = hb::gm_gtime();
+        StagedStore<OUT_DT>::store(r, stage, chunk_count, lane, &tmap_out, col, row0, row0 < M && col < N,
+                                   tr ? &gm_chunk[(c / 32) * 3 + 1] : nullptr);
+        if (tr) gm_chunk[(c / 32) * 3 + 2] = hb::gm_gtime();
+#else
         StagedStore<OUT_DT>::store(r, stage, chunk_count, lane, &tmap_out, col, row0, row0 < M && col < N);
+#endif
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+#ifdef HB_GEMM_TRACE
+      if (threadIdx.x == 64 && tile_iter == 0) gm_epi[1] = hb::gm_gtime();  // this warp's share of the first tile handed to TMA
+#endif
     }
     if (lane == 0) tma_store_wait<0>();  // all output blocks written before the CTA exits
   }
@@ -838,6 +894,16 @@ fp8_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   // ------------------------------- teardown ----------------------------------------------------
   tc_fence_before_sync();
   __syncthreads();
+#ifdef HB_GEMM_TRACE
+  if (threadIdx.x == 32 && leader) {
+    GM_STAMP(7);
+    gm_t[5] = gm_epi[0];
+    gm_t[6] = gm_epi[1];
+    const unsigned int idx = atomicAdd(&g_gemm_trace_n, 1u) % 8192u;
+    for (int i = 0; i < 8; ++i) g_gemm_trace[idx][i] = gm_t[i];
+    for (int i = 0; i < 24; ++i) g_gemm_trace[idx][8 + i] = gm_chunk[i];
+  }
+#endif
   cluster_sync_all();
   if (warp == 1) {
     __syncwarp();
