@@ -12,7 +12,10 @@ back); done one after the other on one stream they take ~15x longer than the 819
 * the device buffers exist ``depth`` times, so the next call's uploads overlap this call's
   downloads;
 * ``y`` may be made resident (:meth:`HostGemm.set_weight`): a weight that is the same for every call is
-  uploaded once, and a call then moves only ``x`` up and ``out`` back.
+  uploaded once, and a call then moves only ``x`` up and ``out`` back;
+* with a process group (one rank per GPU of a node, every rank holding the same ``y`` in host memory and its own
+  rows of ``x``), every rank uploads only its 1/world share of ``y`` and the ranks exchange the shares with one
+  NCCL all-gather over NVLink: the node moves ``y`` over PCIe once per call instead of once per GPU.
 
 The arithmetic is that of :func:`helion_b200.ops.fp8_gemm` on every row block, so the result is
 bit-identical to one call on the whole matrix.
@@ -36,7 +39,7 @@ class HostGemm:
     """
 
     def __init__(self, m: int, n: int, k: int, *, out_dtype: torch.dtype = torch.bfloat16, device=None,
-                 row_blocks: int = 8, depth: int = 2) -> None:
+                 row_blocks: int = 8, depth: int = 2, group=None) -> None:
         if not torch.cuda.is_available():
             raise RuntimeError("HostGemm needs a CUDA device; there is no CPU path")
         self.m, self.n, self.k = m, n, k
@@ -61,6 +64,19 @@ class HostGemm:
             t.record_stream(self._out)
         self._w_ready: Optional[torch.cuda.Event] = None
         self._done: List[Optional[torch.cuda.Event]] = [None] * depth
+        # y shared out over the ranks of `group`: rank r uploads rows [r, r + 1) * n / world of the stored y and an
+        # all-gather on a stream of its own completes every rank's copy (all ranks must call submit in step)
+        self._group = group
+        self._world = self._rank = None
+        if group is not None:
+            import torch.distributed as dist
+
+            self._world, self._rank = dist.get_world_size(group), dist.get_rank(group)
+            if n % self._world != 0:
+                raise ValueError(f"sharing y over {self._world} ranks needs N ({n}) to be a multiple of it")
+            self._xchg = torch.cuda.Stream(self.device)
+            for t in self._y:
+                t.record_stream(self._xchg)
 
     def set_weight(self, y_host: torch.Tensor) -> None:
         """Upload ``y`` (stored as ``[N, K]`` bytes, i.e. column-major) once; later calls of :meth:`submit` with
@@ -95,8 +111,22 @@ class HostGemm:
             self._in.wait_event(self._done[slot])  # this slot's previous download must have left the device buffers
         blocks = [(r, min(r + self.block_rows, m)) for r in range(0, m, self.block_rows)]
         arrived = []
+        y_gathered: Optional[torch.cuda.Event] = None
         with torch.cuda.stream(self._in):
-            if y_host is not None:
+            if y_host is not None and self._group is not None:
+                import torch.distributed as dist
+
+                share = n // self._world
+                mine = slice(self._rank * share, (self._rank + 1) * share)
+                yd[mine].copy_(y_host.view(torch.uint8)[mine], non_blocking=True)
+                uploaded = torch.cuda.Event()
+                uploaded.record(self._in)
+                self._xchg.wait_event(uploaded)
+                with torch.cuda.stream(self._xchg):  # in place: this rank's share already sits where it belongs
+                    dist.all_gather_into_tensor(yd, yd[mine], group=self._group)
+                    y_gathered = torch.cuda.Event()
+                    y_gathered.record(self._xchg)
+            elif y_host is not None:
                 yd.copy_(y_host.view(torch.uint8), non_blocking=True)
             else:
                 yd = self._w
@@ -109,6 +139,8 @@ class HostGemm:
         y_op = yd.view(torch.float8_e4m3fn).t()
         computed = []
         with torch.cuda.stream(self._compute):
+            if y_gathered is not None:
+                self._compute.wait_event(y_gathered)
             for (r0, r1), ev in zip(blocks, arrived):
                 self._compute.wait_event(ev)
                 ops.fp8_gemm(xd[r0:r1].view(torch.float8_e4m3fn), y_op, out_dtype=self.out_dtype, out=od[r0:r1])
@@ -137,7 +169,7 @@ class HostGemm:
     def close(self) -> None:
         """Wait for everything in flight; call before dropping a pipeline whose last results were not awaited."""
         self.synchronize()
-        for stream in (self._in, self._compute, self._out):
+        for stream in (self._in, self._compute, self._out, *((self._xchg,) if self._group is not None else ())):
             stream.synchronize()
 
     def __del__(self) -> None:

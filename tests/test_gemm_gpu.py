@@ -272,6 +272,61 @@ def test_host_buffer_pipeline_equals_the_direct_call(hb):
         pipe.submit(x_pin[:8], y_pin, outs[0])
 
 
+_SHARED_Y_RANK = r"""
+import os, sys
+import torch
+import torch.distributed as dist
+sys.path.insert(0, os.environ["HB_ROOT"])
+import helion_b200 as hb
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", init_method="tcp://127.0.0.1:" + os.environ["HB_PORT"], rank=rank, world_size=world)
+m, n, k = 1024, 768, 640
+g = torch.Generator().manual_seed(77)
+x = torch.randn(m, k, generator=g).to(torch.float8_e4m3fn)
+y = torch.randn(n, k, generator=g).to(torch.float8_e4m3fn)          # stored [N, K]: column-major y
+rows = m // world
+mine = x[rank * rows:(rank + 1) * rows].contiguous()
+want = hb.fp8_gemm(mine.cuda(), y.cuda().t(), out_dtype=torch.bfloat16).cpu()
+x_pin, y_pin = mine.view(torch.uint8).pin_memory(), y.view(torch.uint8).pin_memory()
+pipe = hb.HostGemm(rows, n, k, out_dtype=torch.bfloat16, row_blocks=2, group=dist.group.WORLD)
+outs = [torch.empty(rows, n, dtype=torch.bfloat16).pin_memory() for _ in range(5)]
+events = [pipe.submit(x_pin, y_pin, out) for out in outs]           # more calls in flight than device copies
+for ev, out in zip(events, outs):
+    ev.synchronize()
+    assert torch.equal(out, want), "rank %d" % rank
+pipe.close()
+dist.barrier()
+dist.destroy_process_group()
+print("SHARED_Y_OK", rank, flush=True)
+"""
+
+
+def test_host_buffer_pipeline_shares_y_over_the_ranks(hb):
+    """HostGemm(group=...): every rank uploads 1/world of y and an NCCL all-gather completes it on every GPU.  One
+    process per GPU (two where the machine has them, else a group of one), each comparing its rows with the direct
+    call; ranks only ever leave after a barrier, with nothing in flight."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    world = min(2, torch.cuda.device_count())
+    env = dict(os.environ, WORLD_SIZE=str(world), HB_ROOT=str(Path(__file__).resolve().parent.parent), HB_PORT="29631",
+               NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, "-c", _SHARED_Y_RANK], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outs = []
+    for p in procs:
+        try:
+            outs.append(p.communicate(timeout=240)[0])
+        except subprocess.TimeoutExpired:
+            p.kill()
+            outs.append(p.communicate()[0] + "\n[timed out]")
+    for r, (p, text) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and f"SHARED_Y_OK {r}" in text, text[-2000:]
+
+
 def test_split_k_needs_its_workspace(hb):
     from helion_b200 import _lib
 
