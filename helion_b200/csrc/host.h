@@ -185,7 +185,11 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, 
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
+#ifdef HB_NO_PDL  // development builds only: plain in-order launches, to measure what the early launch is worth
+  cfg.numAttrs = 0;
+#else
   cfg.numAttrs = 1;
+#endif
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
