@@ -65,6 +65,10 @@ extern "C" {
  *      (FP16 is what the reference produces).
  *   K % 16 == 0, N % 8 == 0, M >= 1.
  *   cfg_id: index into the tile-config table, or -1 to let the library choose from the table.
+ *      Every row computes the same product in stream order, with one exception that is never chosen
+ *      automatically: row 23 (few rows of x, for chains of launches) starts reading y before the kernel
+ *      that precedes it on the stream has ended.  Choosing it states that that kernel does not write y
+ *      (y is a weight); x is read, and out written, only after the predecessor has ended.
  *   workspace: scratch for split-K configurations (fp32 partial sums), may be NULL when
  *      hb200_fp8_gemm_workspace_bytes() returns 0 for the configuration.
  */
