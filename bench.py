@@ -496,6 +496,16 @@ def main() -> None:
                 "algorithmic_bytes_per_launch": rows * K + K * N + 2 * rows * N,
             },
         }
+        if extras.get("attention"):
+            # the other kernels of the metric, beside the dominant one: attention against nominal FP8 and against the
+            # softmax-only ceiling measured in this run, the few-row GEMM against the measured HBM bandwidth
+            line["roofline"]["other_kernels"] = {
+                **{name: {k: v.get(k) for k in ("ms", "tflops", "frac_of_nominal_4500", "frac_of_measured_fp8_peak",
+                                                "softmax_ceiling_ms", "frac_of_softmax_ceiling")}
+                   for name, v in extras["attention"].items()},
+                **{f"mlp_{m}": {k: v.get(k) for k in ("ms", "tflops", "hbm_gbs", "frac_of_measured_hbm", "frac_of_measured_fp8_peak")}
+                   for m, v in extras.get("mlp_K4096_N14336", {}).items()},
+            }
         if world == 1:
             line["cpu_baseline"] = {
                 "value": cpu_tflops,
@@ -827,6 +837,24 @@ def run_extras(hb, _lib, o, torch, dev, flush, fp8_peak, peaks) -> dict:
                 "frac_of_nominal_4500": tf / NOMINAL_FP8_TFLOPS, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
 
     res["attention"] = {name: entry(name) for name in ATTN_SHAPES}
+    # The attention kernels' own roofline, measured in this run: the softmax-only kernel (the per-score work of the
+    # reference's loop with two warpgroups per SM and nothing else) gives the time one 128x128 step cannot beat;
+    # a shape's steps spread evenly over the SMs times that is the shortest kernel any pipeline could reach.
+    try:
+        from helion_b200 import ceiling
+
+        row = ceiling.measure(steps=1000, device=dev.index or 0, only=[2])[0]
+        n_sms = _lib.load().hb200_num_sms(dev.index or 0)
+        for name, (b, h, s_len, d) in ATTN_SHAPES.items():
+            steps = b * h * (s_len // 128) * (s_len // 128)
+            ceiling_ms = steps / n_sms * row["ns_per_step_per_sm"] * 1e-6
+            res["attention"][name]["softmax_ceiling_ms"] = ceiling_ms
+            res["attention"][name]["frac_of_softmax_ceiling"] = ceiling_ms / res["attention"][name]["ms"]
+        res["attention_softmax_ceiling"] = {"cycles_per_128x128_step_per_sm": row["cycles_per_step_per_sm"],
+                                            "ns_per_128x128_step_per_sm": row["ns_per_step_per_sm"],
+                                            "how": "helion_b200.ceiling, two softmax warpgroups per SM, all exp2 on MUFU, 1000 steps"}
+    except Exception as ex:  # context only
+        res["attention_softmax_ceiling"] = {"error": str(ex)[:120]}
     res["attention_causal"] = {name: entry(name) for name in CAUSAL}  # FLOPs counted under the mask only
     res["mlp_K4096_N14336"] = {f"M{m}": entry(f"mlp_M{m}") for m in MLP_M}
     # the callers either side of the two kernels: scaled GEMM epilogue, attention input preparation

@@ -40,15 +40,16 @@ VARIANTS = [
 ]
 
 
-def measure(steps: int = 2000, device: int = 0):
-    """Returns one dict per variant: cycles per 128x128 step per SM (from the SM clock) and the event time."""
+def measure(steps: int = 2000, device: int = 0, only=None):
+    """Returns one dict per variant: cycles per 128x128 step per SM (from the SM clock) and the event time.
+    ``only``: indices into ``VARIANTS`` to run (default: all)."""
     lib = _lib.load()
     dev = torch.device("cuda", device)
     n_sms = lib.hb200_num_sms(device)
     _lib.raise_for(n_sms, "num_sms")
     stream = torch.cuda.current_stream(device).cuda_stream
     rows = []
-    for label, wgs, ctas, poly, mode in VARIANTS:
+    for label, wgs, ctas, poly, mode in (VARIANTS if only is None else [VARIANTS[i] for i in only]):
         cycles = torch.zeros(n_sms * ctas, dtype=torch.int64, device=dev)
         for _ in range(2):  # first launch loads the kernel
             _lib.raise_for(lib.hb200_debug_softmax_ceiling(wgs, ctas, poly, mode, steps, cycles.data_ptr(), device, stream),
