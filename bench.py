@@ -389,7 +389,7 @@ def main() -> None:
     # NCCL all-gather over NVLink per step completes every GPU's copy, so the node moves y over PCIe once per step
     # instead of once per GPU (HostGemm(..., group=...)).  Same inputs in host memory, same result in host memory.
     e2e_every_rank = None
-    if world > 1:
+    if world > 1 and N % world == 0:
         e2e_every_rank = {"value": e2e_value, "ms_per_step": e2e_ms, "h2d_bytes_per_step": int(x_pin.numel() + y_pin.numel())}
         out_pin.zero_()
         shared = hb.HostGemm(rows, N, K, out_dtype=torch.bfloat16, device=dev, group=dist.group.WORLD)
@@ -456,9 +456,9 @@ def main() -> None:
             "e2e": {
                 "value": e2e_value,
                 "unit": "TFLOP/s",
-                "h2d_bytes_per_step": int(x_pin.numel() + y_pin.numel() // world),
+                "h2d_bytes_per_step": int(x_pin.numel() + (y_pin.numel() // world if e2e_every_rank is not None else y_pin.numel())),
                 "d2h_bytes_per_step": int(out_pin.numel() * 2),
-                "bytes_are": "per rank" + ("" if world == 1 else
+                "bytes_are": "per rank" + ("" if e2e_every_rank is None else
                                            "; every rank uploads 1/world of y and one NCCL all-gather over NVLink per step "
                                            "completes it on every GPU (HostGemm(group=...))"),
                 "steps": e2e_steps,
