@@ -74,6 +74,50 @@ def test_random_fp8_gemm(hb, m, n, k, colmajor, pad_x, pad_y, dt, scaled, seed):
     assert o.rel_frobenius(got, exact) <= (2.5e-3 if dt == torch.bfloat16 else 1e-3)
 
 
+def _row_cases(count, seed):
+    rng = random.Random(seed)
+    for i in range(count):
+        few = rng.random() < 0.4
+        row = rng.choice([18, 22, 23]) if few else rng.choice([6, 14, 21])
+        m = rng.choice([1, 7, 16, 33, 64]) if few else rng.choice([130, 300, 513, 1000, 1500])
+        n = 8 * rng.randint(1, 170)
+        k = 16 * rng.randint(1, 64)
+        pad_x = 16 * rng.randint(0, 2)
+        pad_y = 16 * rng.randint(0, 2)
+        dt = rng.choice([torch.float16, torch.bfloat16, torch.float32])
+        scaled = rng.choice([None, None, "tensor", "rows"])
+        yield pytest.param(row, m, n, k, pad_x, pad_y, dt, scaled, 3000 + i, id=f"row{row}-{m}x{n}x{k}-{NAME[dt]}-{scaled}")
+
+
+@pytest.mark.parametrize("row,m,n,k,pad_x,pad_y,dt,scaled,seed", list(_row_cases(30, seed=515)))
+def test_random_fp8_gemm_on_explicit_table_rows(hb, row, m, n, k, pad_x, pad_y, dt, scaled, seed):
+    """The rows the automatic choice reaches only for particular shapes -- the CTA-pair tiles (6, 14, the 224-wide
+    21) and the few-row kernels (18 and its chain forms 22 / 23) -- on ragged sizes, padded leading dimensions,
+    every output type and both scale modes, column-major y."""
+    x, y = o.gemm_inputs(m, n, k, seed=seed)
+    xbuf = torch.zeros(m, k + pad_x, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    xbuf[:, :k] = x
+    xd = xbuf.cuda()[:, :k]
+    ybuf = torch.zeros(n, k + pad_y, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    ybuf[:, :k] = y.t()
+    yd = ybuf.cuda()[:, :k].t()
+    xb, yb = o.torch_fp8_to_bits(x), o.torch_fp8_to_bits(y)
+    g = torch.Generator().manual_seed(seed)
+    if scaled is None:
+        got = hb.fp8_gemm(xd, yd, out_dtype=dt, config=row)
+        want = o.fp8_gemm(xb, yb, NAME[dt])
+        exact = o.fp8_gemm(xb, yb, "fp32")
+    else:
+        sa = torch.rand(1 if scaled == "tensor" else m, 1, generator=g) + 0.5
+        sb = torch.rand(1, 1 if scaled == "tensor" else n, generator=g) + 0.5
+        got = hb.fp8_gemm(xd, yd, out_dtype=dt, scale_a=sa.cuda(), scale_b=sb.cuda(), config=row)
+        want = o.fp8_gemm_scaled(xb, yb, sa.numpy(), sb.numpy(), NAME[dt])
+        exact = o.fp8_gemm_scaled(xb, yb, sa.numpy(), sb.numpy(), "fp32")
+    got = got.float().cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=2e-2, atol=2e-2)
+    assert o.rel_frobenius(got, exact) <= (2.5e-3 if dt == torch.bfloat16 else 1e-3)
+
+
 def _attn_cases(count, seed):
     rng = random.Random(seed)
     for i in range(count):
