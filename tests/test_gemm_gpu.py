@@ -311,8 +311,13 @@ def test_host_buffer_pipeline_shares_y_over_the_ranks(hb):
     import sys
     from pathlib import Path
 
+    import socket
+
     world = min(2, torch.cuda.device_count())
-    env = dict(os.environ, WORLD_SIZE=str(world), HB_ROOT=str(Path(__file__).resolve().parent.parent), HB_PORT="29631",
+    with socket.socket() as sock:  # a port nobody listens on right now
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    env = dict(os.environ, WORLD_SIZE=str(world), HB_ROOT=str(Path(__file__).resolve().parent.parent), HB_PORT=str(port),
                NCCL_NVLS_ENABLE="0")
     procs = [subprocess.Popen([sys.executable, "-c", _SHARED_Y_RANK], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
                               stderr=subprocess.STDOUT, text=True) for r in range(world)]
