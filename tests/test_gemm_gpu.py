@@ -253,6 +253,34 @@ def test_output_scales(hb, m, n, k, config):
         hb.fp8_gemm(xd, yd, scale_a=one.half(), scale_b=one)
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 512, 1024), (300, 784, 640), (16, 14336, 4096), (2048, 1024, 512)])
+@pytest.mark.parametrize("mode", ["tensor", "rows"])
+def test_output_scales_against_atens_cuda_scaled_mm(hb, m, n, k, mode):
+    """The caller this entry point replaces is ``torch._scaled_mm(x, y, scale_a, scale_b)`` (the reference's baseline,
+    examples/fp8_gemm.py:61-78, calls it with both scales 1.0).  Same operands, same scales, bf16 out, on the same
+    GPU: the two must agree to the output rounding -- the summation order inside the tensor cores differs, so a
+    result that sits on a rounding boundary may land on either side: nearly all outputs identical, none further
+    apart than one bf16 step."""
+    x, y = o.gemm_inputs(m, n, k, seed=4100 + m + n, weight_like=(n == 14336))
+    xd, yd = to_dev(x), to_dev(y)
+    g = torch.Generator().manual_seed(m + n + k)
+    sa = (torch.rand(1 if mode == "tensor" else m, 1, generator=g) + 0.5).cuda()
+    sb = (torch.rand(1, 1 if mode == "tensor" else n, generator=g) + 0.5).cuda()
+    try:
+        if mode == "tensor":
+            want = torch._scaled_mm(xd, yd, sa.reshape(()), sb.reshape(()), out_dtype=torch.bfloat16)
+        else:
+            want = torch._scaled_mm(xd, yd, sa, sb, out_dtype=torch.bfloat16)
+    except (RuntimeError, ValueError, TypeError) as e:
+        pytest.skip(f"this torch build has no such _scaled_mm on CUDA: {str(e)[:80]}")
+    got = hb.fp8_gemm(xd, yd, out_dtype=torch.bfloat16, scale_a=sa, scale_b=sb)
+    same = (got.view(torch.int16) == want.view(torch.int16)).float().mean().item()
+    assert same >= 0.98, same
+    gf, wf = got.float(), want.float()
+    step = wf.abs().clamp_min(1e-30) * 2.0 ** -7  # one bf16 step at the value's magnitude (8 significant bits)
+    assert bool(((gf - wf).abs() <= step + 1e-6).all()), float(((gf - wf).abs() / step).max())
+
+
 def test_host_buffer_pipeline_equals_the_direct_call(hb):
     """HostGemm (pinned operands in, pinned result out, row blocks on three streams, double-buffered
     device copies) must give exactly what one fp8_gemm call on the whole matrix gives."""
