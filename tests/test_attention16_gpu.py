@@ -88,3 +88,21 @@ def test_full_size_properties(hb):
         np.testing.assert_allclose(out[b, h].cpu().numpy(), raw[0], rtol=2e-2, atol=2e-2)
     perm = torch.randperm(48, device="cuda", generator=torch.Generator(device="cuda").manual_seed(9))
     assert torch.equal(hb.attention(q[:, perm], k[:, perm], v[:, perm]), hb.attention(q, k, v)[:, perm])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("b,h,s,d", [(2, 4, 512, 64), (1, 8, 1024, 128), (2, 2, 200, 64)])
+def test_against_atens_attention_on_the_gpu(hb, b, h, s, d, dtype):
+    """What the reference's own example checks against (examples/attention.py:128-145: a matmul / softmax / matmul
+    baseline and ``torch.nn.functional.scaled_dot_product_attention``, through run_example with rtol 1e-2, atol
+    1e-1): both on the same GPU, held to allclose(2e-2, 2e-2) here."""
+    g = torch.Generator().manual_seed(9000 + s + d)
+    q, k, v = (torch.randn(b, h, s, d, generator=g).to(dtype).cuda() for _ in range(3))
+    got = hb.attention(q, k, v)
+    sdpa = torch.nn.functional.scaled_dot_product_attention(q, k, v)
+    p = torch.softmax(torch.matmul(q.float(), k.float().transpose(2, 3)) / (d ** 0.5), dim=-1)
+    plain = torch.matmul(p, v.float())
+    torch.testing.assert_close(got, sdpa, rtol=1e-2, atol=1e-1)  # the reference's gate
+    torch.testing.assert_close(got.float(), sdpa.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(got.float(), plain, rtol=2e-2, atol=2e-2)
+
