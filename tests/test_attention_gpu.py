@@ -434,3 +434,29 @@ class TestFullSize:
             lo, hi = shard_range(192, 8, rank)
             part = sharded_fp8_attention(qd, kd, vd, 4, 48, rank=rank, world_size=8)
             assert torch.equal(part.view(torch.uint8), full[lo:hi])
+
+
+@pytest.mark.parametrize("sq,sk,dim,causal", [(256, 256, 64, True), (128, 384, 64, True), (200, 328, 128, True),
+                                              (192, 512, 128, False), (1024, 1024, 64, True)])
+def test_mask_and_key_length_against_atens_attention_on_the_gpu(hb, sq, sk, dim, causal):
+    """The mask and the separate key length have no counterpart in the reference's fp8 kernel, so the oracle for them
+    is an extension; this pins their MEANING against an independent implementation: ATen's
+    scaled_dot_product_attention on the same GPU, fp32, on the dequantised inputs, with the mask written out as a
+    boolean matrix (key j visible to query i when j <= i + (seq_k - seq_q)).  The fp8 kernel rounds P to e4m3, so
+    the gate is the one the reference's own test uses for its fp8 kernel against a PyTorch baseline
+    (test/test_examples.py:577-614: atol 0.2, rtol 0.1), tightened to 0.1 / 0.1; a mask that is off by one row or
+    aligned to the wrong corner moves outputs by O(1)."""
+    batch, heads = 2, 3
+    g = torch.Generator().manual_seed(sq * 7 + sk + dim)
+    q = torch.randn(batch * heads, sq, dim, generator=g).to(torch.float8_e4m3fn).cuda()
+    k = torch.randn(batch * heads, sk, dim, generator=g).to(torch.float8_e4m3fn).cuda()
+    v = torch.randn(batch * heads, sk, dim, generator=g).to(torch.float8_e4m3fn).cuda()
+    got = hb.fp8_attention(q, k, v.permute(0, 2, 1), batch, heads, out_dtype=torch.float32, causal=causal)
+    mask = None
+    if causal:
+        i = torch.arange(sq, device="cuda")[:, None]
+        j = torch.arange(sk, device="cuda")[None, :]
+        mask = j <= i + (sk - sq)
+    want = torch.nn.functional.scaled_dot_product_attention(q.float()[None], k.float()[None], v.float()[None], attn_mask=mask)[0]
+    torch.testing.assert_close(got.reshape(batch * heads, sq, dim), want, rtol=0.1, atol=0.1)
+
