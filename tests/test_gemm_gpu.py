@@ -281,6 +281,23 @@ def test_output_scales_against_atens_cuda_scaled_mm(hb, m, n, k, mode):
     assert bool(((gf - wf).abs() <= step + 1e-6).all()), float(((gf - wf).abs() / step).max())
 
 
+@pytest.mark.parametrize("m,n,k", [(8192, 8192, 8192), (1024, 8192, 8192), (2048, 14336, 4096)])
+def test_full_size_products_against_atens_cuda_scaled_mm(hb, m, n, k):
+    """The whole benchmark-size product (BASELINE config 2, its 8-GPU row shard -- the 512x224 table row -- and an MLP
+    shape) against the reference's GPU baseline, ``torch._scaled_mm`` with unit scales (examples/fp8_gemm.py:61-78),
+    every output: none further apart than one bf16 step, at least 98 % bit-identical."""
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    x = torch.randn(m, k, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    y = torch.randn(n, k, device="cuda", generator=g).to(torch.float8_e4m3fn).t()
+    one = torch.ones((), device="cuda")
+    want = torch._scaled_mm(x, y, one, one, out_dtype=torch.bfloat16)
+    got = hb.fp8_gemm(x, y, out_dtype=torch.bfloat16)
+    assert (got.view(torch.int16) == want.view(torch.int16)).float().mean().item() >= 0.98
+    gf, wf = got.float(), want.float()
+    worst = ((gf - wf).abs() / (wf.abs().clamp_min(1e-30) * 2.0 ** -7 + 1e-6)).max().item()
+    assert worst <= 1.0, worst
+
+
 def test_host_buffer_pipeline_equals_the_direct_call(hb):
     """HostGemm (pinned operands in, pinned result out, row blocks on three streams, double-buffered
     device copies) must give exactly what one fp8_gemm call on the whole matrix gives."""
