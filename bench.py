@@ -111,24 +111,35 @@ class ClockSampler:
                     for name, bit in names.items():
                         if mask & bit:
                             self.reasons.add(name)
-                self.samples.append((power, sm))
+                self.samples.append((power, sm, time.perf_counter()))
                 n += 1
             except Exception:
                 pass
             if self.period_s >= 0.001:
                 time.sleep(self.period_s)
 
-    def stop(self) -> dict:
+    def stop(self, window=None) -> dict:
+        """Ends the sampling.  `window` = (t0, t1) in time.perf_counter() seconds keeps only the samples taken inside
+        it (the thread is started a little before the timed region so that it is surely running when that begins)."""
         if self._nvml is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"], "samples": 0}
         self._stop.set()
         self._thread.join(timeout=2)
-        sm = [s for _, s in self.samples]
+        where = "the whole sampling period"
+        if window is not None:
+            inside = [s for s in self.samples if window[0] <= s[2] <= window[1]]
+            where = f"inside the timed region of {(window[1] - window[0]) * 1e3:.2f} ms"
+            if not inside:  # a region shorter than one query: the nearest sample stands in, and the line says so
+                inside = sorted(self.samples, key=lambda s: min(abs(s[2] - window[0]), abs(s[2] - window[1])))[:1]
+                where = f"nearest to the timed region of {(window[1] - window[0]) * 1e3:.2f} ms (none fell inside)"
+            self.samples = inside
+        sm = [s[1] for s in self.samples]
         return {
+            "samples_taken": where,
             "sm_mhz": statistics.median(sm) if sm else None,
             "sm_min_mhz": min(sm) if sm else None,
             "sm_max_mhz": self.sm_max,
-            "power_w_max": max(p for p, _ in self.samples) if self.samples else None,
+            "power_w_max": max(s[0] for s in self.samples) if self.samples else None,
             "samples": len(sm),
             "reasons": sorted(self.reasons),
         }
@@ -314,14 +325,19 @@ def main() -> None:
     sampler = ClockSampler(local_rank, period_s=0.0005)
     if rank == 0:
         sampler.start()
+        time.sleep(0.02)  # the sampling thread is up and has made its first queries before the region starts
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     ev_a = torch.cuda.Event(enable_timing=True)
     ev_b = torch.cuda.Event(enable_timing=True)
+    t_region0 = time.perf_counter()
     ev_a.record()
     for i in range(args.steps):
         step(warmup + i)
     ev_b.record()
     torch.cuda.synchronize()
+    t_region1 = time.perf_counter()
     if world > 1:
         dist.barrier()
     total_ms = ev_a.elapsed_time(ev_b)
@@ -329,7 +345,7 @@ def main() -> None:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms_max = float(t.item())
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(window=(t_region0, t_region1)) if rank == 0 else None
     _lib.check_status(local_rank)
     ms_per_step = total_ms_max / args.steps
     value = GEMM_FLOPS / (ms_per_step * 1e-3) / 1e12  # the whole job: all ranks' rows of the one 8192^3 product
